@@ -53,9 +53,11 @@ Json spec_json(const ModelSpec& spec) {
         Json cj = Json::object();
         cj.set("layer", c.layer);
         cj.set("cache_from", c.cache_from >= 0 ? Json(c.cache_from) : Json());
+        cj.set("pass", c.pass);
         sched.push(cj);
     }
     j.set("schedule", sched);
+    j.set("keep_embedding_output", spec.keep_embedding_output);
     j.set("final_norm", spec.final_norm.to_json());
     j.set("head", spec.head.to_json());
     return j;

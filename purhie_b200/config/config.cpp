@@ -334,6 +334,7 @@ ModelSpec Qwen3Config::build_spec() const {
 
 void register_bozosun_architecture();
 void register_sizizen_architecture();
+void register_zerusun_architecture();
 
 void register_builtin_architectures() {
     static std::once_flag once;
@@ -341,6 +342,7 @@ void register_builtin_architectures() {
         register_architecture("Qwen3ForCausalLM", Qwen3Config::read);
         register_bozosun_architecture();
         register_sizizen_architecture();
+        register_zerusun_architecture();
     });
 }
 

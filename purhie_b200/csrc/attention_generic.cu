@@ -2,7 +2,8 @@
 // arithmetic.  It is the whole attention of the 32-bit path, the reference the fast kernels are tested
 // against, and the refuge for head sizes the fast kernels do not take.
 //
-// Values may have another width (DV) than keys (D); the output row of a head is DV wide.
+// Values may have another width (DV) than keys (D); the output row of a head is DV wide.  A value row may also be the
+// first DV elements of a wider row (v_stride elements from one token's to the next's): values kept inside the key rows.
 // One warp per (token row, query head).  The row at absolute position z of a request sees the cached
 // positions lo .. z, lo = max(0, z - window + 1) (window 0: lo = 0); with a block mask (chunk > 0) it sees only
 // the positions of its own block of `chunk` positions counted from 0, lo = max(lo, floor(z / chunk) * chunk).
@@ -22,14 +23,14 @@ namespace {
 using namespace ph;
 
 constexpr int WARPS = 4;
-constexpr int MAX_D = 512;
+constexpr int MAX_D = 640;
 
 template <typename TQ, typename TKV, typename TO>
 __global__ void attention_generic_kernel(const TQ* __restrict__ q, const TKV* __restrict__ k_base,
                                          const TKV* __restrict__ v_base, long long page_stride, int page_size,
                                          const int32_t* __restrict__ block_table, int table_stride,
                                          const int32_t* __restrict__ row_seg, const int32_t* __restrict__ positions,
-                                         TO* __restrict__ out, int T, int HQ, int HKV, int D, int window, float scale, int DV, int chunk) {
+                                         TO* __restrict__ out, int T, int HQ, int HKV, int D, int window, float scale, int DV, int chunk, int VS) {
     __shared__ float qs[WARPS][MAX_D];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long item = (long long)blockIdx.x * WARPS + warp;
@@ -57,7 +58,7 @@ __global__ void attention_generic_kernel(const TQ* __restrict__ q, const TKV* __
             const int page = table[p / page_size];
             const size_t at = (size_t)g * page_size + p % page_size;
             const TKV* krow = k_base + (size_t)page * page_stride + at * D;
-            vrow = v_base + (size_t)page * page_stride + at * DV;
+            vrow = v_base + (size_t)page * page_stride + at * VS;
             float dot = 0.0f;
             for (int d = 0; d < D; ++d) dot += qs[warp][d] * to_float<TKV>(krow[d]);
             s = dot * scale;
@@ -96,13 +97,14 @@ PH_EXPORT int ph_attention_generic(const void* q, int q_dtype, const void* k_bas
                                    long long page_stride, int page_size, const int32_t* block_table,
                                    int table_stride, const int32_t* row_seg, const int32_t* positions, void* out,
                                    int out_dtype, int T, int HQ, int HKV, int D, int window, float scale, int DV,
-                                   int chunk, cudaStream_t stream) {
+                                   int chunk, int v_stride, cudaStream_t stream) {
     if (!q || !k_base || !v_base || !block_table || !row_seg || !positions || !out || T < 0 || HQ < 1 || HKV < 1 ||
         D < 1 || page_size < 1 || window < 0 || chunk < 0 || !valid_dtype(q_dtype) || !valid_dtype(kv_dtype) ||
         !valid_dtype(out_dtype))
         return fail(PH_ERR_ARG, "attention_generic: bad arguments (T %d, HQ %d, HKV %d, D %d)", T, HQ, HKV, D);
     if (HQ % HKV) return fail(PH_ERR_ARG, "attention_generic: %d query heads are not a multiple of %d kv heads", HQ, HKV);
     if (DV <= 0) DV = D;                     // values as wide as keys
+    if (v_stride <= 0) v_stride = DV;        // value rows lie side by side (else: v_stride elements apart, inside wider rows)
     if (D > MAX_D || DV > MAX_D) return fail(PH_ERR_UNSUPPORTED, "attention_generic: head_dim %d / %d exceeds the supported %d", D, DV, MAX_D);
     if (T == 0) return PH_OK;
     const long long items = (long long)T * HQ;
@@ -110,7 +112,7 @@ PH_EXPORT int ph_attention_generic(const void* q, int q_dtype, const void* k_bas
 #define LAUNCH(TQ, TKV, TO)                                                                                    \
     attention_generic_kernel<TQ, TKV, TO><<<blocks, WARPS * 32, 0, stream>>>(                                  \
         (const TQ*)q, (const TKV*)k_base, (const TKV*)v_base, page_stride, page_size, block_table, table_stride, \
-        row_seg, positions, (TO*)out, T, HQ, HKV, D, window, scale, DV, chunk)
+        row_seg, positions, (TO*)out, T, HQ, HKV, D, window, scale, DV, chunk, v_stride)
     PH_DISPATCH(q_dtype, TQ, PH_DISPATCH(kv_dtype, TKV, PH_DISPATCH(out_dtype, TO, LAUNCH(TQ, TKV, TO))));
 #undef LAUNCH
     return check_launch("attention_generic");

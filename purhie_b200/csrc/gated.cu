@@ -2,6 +2,7 @@
 // SwiGLU kernel reads them), with the gate's family as a parameter:
 //   kind 0 (silu):           out = g / (1 + exp(-g)) * u
 //   kind 1 (clamped swish):  g' = min(g, limit), u' = clamp(u, -limit, limit), out = g' * sigmoid(alpha * g') * (u' + shift)
+//   kind 2 (gelu, tanh form): out = 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))) * u
 // and activations of one argument over plain rows (unary_act): kind 0 silu, kind 1 the square of relu.
 // The sums over split-K partial results and the activation are float32.
 #include "common.cuh"
@@ -12,6 +13,7 @@ using namespace ph;
 
 __device__ __forceinline__ float gated(float g, float u, int kind, float alpha, float limit, float shift) {
     if (kind == 0) return g / (1.0f + expf(-g)) * u;
+    if (kind == 2) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
     g = fminf(g, limit);
     u = fminf(fmaxf(u, -limit), limit);
     return g / (1.0f + expf(-alpha * g)) * (u + shift);
@@ -111,7 +113,7 @@ PH_EXPORT int ph_unary_act(const void* in, int in_dtype, int splits, long long s
 
 PH_EXPORT int ph_glu(const void* gate_up, int in_dtype, int splits, long long split_stride, void* out, int out_dtype, int T,
                      int FF, int kind, float alpha, float limit, float shift, cudaStream_t stream) {
-    if (!gate_up || !out || T < 0 || FF < 1 || splits < 1 || kind < 0 || kind > 1 || !valid_dtype(in_dtype) || !valid_dtype(out_dtype))
+    if (!gate_up || !out || T < 0 || FF < 1 || splits < 1 || kind < 0 || kind > 2 || !valid_dtype(in_dtype) || !valid_dtype(out_dtype))
         return fail(PH_ERR_ARG, "glu: bad arguments (T %d, FF %d, kind %d)", T, FF, kind);
     const long long total = (long long)T * FF;
     if (total == 0) return PH_OK;

@@ -33,11 +33,15 @@ ERRORS = {101: "the TMA producer waited too long for a free stage", 102: "the MM
 
 
 def _gate_pointer(gate):
-    """``gate``: None (the silu gate) or (alpha, limit, shift) of the clamped swish, as three floats on the host."""
+    """``gate``: None (the silu gate), (alpha, limit, shift) of the clamped swish, or "gelu_tanh"; the kernel reads four
+    floats on the host: alpha, limit, shift and the gate's kind (1 clamped swish, 2 the tanh form of gelu)."""
     if gate is None:
         return None
     import ctypes
-    arr = (ctypes.c_float * 3)(*[float(v) for v in gate])
+    values = [0.0, 0.0, 0.0, 2.0] if isinstance(gate, str) else [float(v) for v in gate] + [1.0]
+    if isinstance(gate, str) and gate != "gelu_tanh":
+        raise ValueError(f"gate '{gate}' is not known")
+    arr = (ctypes.c_float * 4)(*values)
     _gate_pointer.keep = arr                       # alive until the call has read it
     return ctypes.addressof(arr)
 

@@ -210,6 +210,8 @@ __device__ __forceinline__ float plain_row_factor(const GemmParams& p, int a) {
 // The gated activation of a (gate, up) pair, by the family the parameters name.
 __device__ __forceinline__ float gate_times(const GemmParams& p, float g, float u) {
     if (p.gate_kind == 0) return g / (1.0f + __expf(-g)) * u;
+    // the tanh form of gelu: 0.5 g (1 + tanh(y)) = g sigmoid(2 y), y = sqrt(2/pi) (g + 0.044715 g^3)
+    if (p.gate_kind == 2) return g / (1.0f + __expf(-1.5957691216057308f * (g + 0.044715f * g * g * g))) * u;
     g = fminf(g, p.gate_limit);
     u = fminf(fmaxf(u, -p.gate_limit), p.gate_limit);
     return g / (1.0f + __expf(-p.gate_alpha * g)) * (u + p.gate_shift);
@@ -1177,7 +1179,7 @@ PH_EXPORT int ph_gemm_bf16_tcgen05_pair(const void* x, const void* w, void* out,
     GemmParams p;
     p.rows_a = M; p.rows_b = N; p.K = K;
     p.a_tiles = 0; p.b_tiles = (N + PAIR_BN - 1) / PAIR_BN; p.splits = splits; p.kblocks = kblocks;
-    p.out = out; p.out_bf16 = out_dtype == PH_BF16; p.swapped = 0; p.swiglu = swiglu; p.gate_kind = gate ? 1 : 0; p.gate_alpha = gate ? gate[0] : 1.0f; p.gate_limit = gate ? gate[1] : 0.0f; p.gate_shift = gate ? gate[2] : 0.0f; p.accumulate = accumulate; p.ld = swiglu ? N / 2 : N;
+    p.out = out; p.out_bf16 = out_dtype == PH_BF16; p.swapped = 0; p.swiglu = swiglu; p.gate_kind = gate ? (int)gate[3] : 0; p.gate_alpha = gate ? gate[0] : 1.0f; p.gate_limit = gate ? gate[1] : 0.0f; p.gate_shift = gate ? gate[2] : 0.0f; p.accumulate = accumulate; p.ld = swiglu ? N / 2 : N;
     p.split_stride = (long long)M * N; p.error_flag = error_flag;
     p.row_sumsq = row_sumsq; p.row_chunks = row_chunks; p.row_width = row_width; p.row_eps = row_eps;
     p.norm_weight = norm_weight; p.norm_rows = (__nv_bfloat16*)norm_rows; p.norm_sumsq = norm_sumsq;
@@ -1196,7 +1198,8 @@ PH_EXPORT int ph_gemm_bf16_tcgen05_pair(const void* x, const void* w, void* out,
 // out[M, N] (or float32 partials [splits][M, N]) = x[M, K] * w[N, K]^T.  swapped: the weight fills the 128-row
 // side of the instruction (few tokens); block_n is the tile size on the other side (16 .. 256, a power of two).
 // swiglu: the rows of w are (gate, up) pairs and out is [M, N / 2] = silu(gate) * up, computed in the epilogue;
-// gate (three floats on the host: alpha, limit, shift; null: the silu gate) makes it the clamped swish of GemmParams
+// gate (four floats on the host: alpha, limit, shift, kind; null: the silu gate) names the gate of GemmParams (kind 1 the
+// clamped swish, 2 the tanh form of gelu)
 // (the formula of src/gpu_ops.hip:103-114 in the reference).
 // accumulate: out (float32, plain orientation, one split, no activation) += the product.
 // row_sumsq [M][row_chunks] (or null), row_width, row_eps: the activations lack a factor per token, see GemmParams;
@@ -1239,7 +1242,7 @@ PH_EXPORT int ph_gemm_bf16_tcgen05(const void* x, const void* w, void* out, int 
     p.rows_a = rows_a; p.rows_b = rows_b; p.K = K;
     p.a_tiles = (rows_a + BM - 1) / BM; p.b_tiles = (rows_b + block_n - 1) / block_n;
     p.splits = splits; p.kblocks = kblocks;
-    p.out = out; p.out_bf16 = out_dtype == PH_BF16; p.swapped = swapped; p.swiglu = swiglu; p.gate_kind = gate ? 1 : 0; p.gate_alpha = gate ? gate[0] : 1.0f; p.gate_limit = gate ? gate[1] : 0.0f; p.gate_shift = gate ? gate[2] : 0.0f; p.accumulate = accumulate; p.ld = swiglu ? N / 2 : N;
+    p.out = out; p.out_bf16 = out_dtype == PH_BF16; p.swapped = swapped; p.swiglu = swiglu; p.gate_kind = gate ? (int)gate[3] : 0; p.gate_alpha = gate ? gate[0] : 1.0f; p.gate_limit = gate ? gate[1] : 0.0f; p.gate_shift = gate ? gate[2] : 0.0f; p.accumulate = accumulate; p.ld = swiglu ? N / 2 : N;
     p.split_stride = (long long)M * N; p.error_flag = error_flag;
     p.row_sumsq = row_sumsq; p.row_chunks = row_chunks; p.row_width = row_width; p.row_eps = row_eps;
     p.norm_weight = norm_weight; p.norm_rows = (__nv_bfloat16*)norm_rows; p.norm_sumsq = norm_sumsq;

@@ -28,6 +28,9 @@ using namespace ph;
 // log(sigmoid(x)) without overflow: -(max(-x, 0) + log1p(exp(-|x|)))
 __device__ __forceinline__ float log_sigmoid(float x) { return -(fmaxf(-x, 0.0f) + log1pf(expf(-fabsf(x)))); }
 
+// what q, k and v pass through on their way into the recurrence: nothing, or silu
+__device__ __forceinline__ float act_in(float x, int kind) { return kind ? x / (1.0f + expf(-x)) : x; }
+
 struct ScanParams {
     const void* q; const void* k; const void* v; const void* g;     // rows of the compute dtype, `stride` elements apart
     long long stride;
@@ -48,6 +51,8 @@ struct ScanParams {
     int cols;                                                        // columns of a head per block
     int tile;                                                        // tokens staged at a time
     int fused_norm;                                                  // the block holds all of a head's columns and norms its rows
+    const float* head_decay;                                         // [H] or null: one constant decay per head instead of the logits
+    int in_act;                                                      // 1: q, k and v pass through silu on their way in
 };
 
 constexpr int DPT = 16;          // key channels per thread
@@ -161,7 +166,7 @@ __global__ void __launch_bounds__(MAX_THREADS, 2) decayed_scan_kernel(ScanParams
             const size_t row = (size_t)(row0 + t0 + tt);
             if (r < D) fetched[u] = raw_bits<TX>(qb + row * p.stride + r);
             else if (r < 2 * D) fetched[u] = raw_bits<TX>(kb + row * p.stride + (r - D));
-            else if (r < 3 * D) fetched[u] = __float_as_uint(zb[row * p.z_stride + (r - 2 * D)]);
+            else if (r < 3 * D) fetched[u] = p.head_decay ? 0u : __float_as_uint(zb[row * p.z_stride + (r - 2 * D)]);
             else if ((int)(blockIdx.z * cols) + r - 3 * D < DV) fetched[u] = raw_bits<TX>(vb + row * p.stride + (r - 3 * D));
         }
     };
@@ -174,12 +179,13 @@ __global__ void __launch_bounds__(MAX_THREADS, 2) decayed_scan_kernel(ScanParams
             if (r < 3 * D) {
                 const int which = which_of(r), d = r - which * D;
                 float val;
-                if (which == 0) val = from_bits<TX>(fetched[u]) * p.q_scale;
-                else if (which == 1) val = from_bits<TX>(fetched[u]);
+                if (which == 0) val = act_in(from_bits<TX>(fetched[u]), p.in_act) * p.q_scale;
+                else if (which == 1) val = act_in(from_bits<TX>(fetched[u]), p.in_act);
+                else if (p.head_decay) val = p.head_decay[h];
                 else val = expf(log_sigmoid(__uint_as_float(fetched[u]) + (p.z_bias ? p.z_bias[(size_t)h * D + d] : 0.0f)) * p.inv_tau);
                 stage[((size_t)(buf * TT + tt) * 3 + which) * SL + (d / DPT) * SLICE + (d % DPT)] = val;
             } else {
-                vs[(size_t)(buf * TT + tt) * cols + (r - 3 * D)] = from_bits<TX>(fetched[u]);
+                vs[(size_t)(buf * TT + tt) * cols + (r - 3 * D)] = act_in(from_bits<TX>(fetched[u]), p.in_act);
             }
         }
     };
@@ -267,6 +273,12 @@ __global__ void chunk_decay_kernel(ScanParams p) {
     for (int d = threadIdx.x; d < p.D; d += blockDim.x) {
         const float bias = p.z_bias ? p.z_bias[(size_t)h * p.D + d] : 0.0f;
         float prod = 1.0f;
+        if (p.head_decay) {                        // the constant, token by token as the recurrence multiplies it
+            const float a = p.head_decay[h];
+            for (int t = 0; t < n; ++t) prod *= a;
+            p.decay[((size_t)item * p.H + h) * p.D + d] = prod;
+            continue;
+        }
         const float* zz = p.z + (size_t)row0 * p.z_stride + (size_t)h * p.D + d;
         for (int t = 0; t < n; t += 8) {
             float x[8];
@@ -379,10 +391,44 @@ __global__ void rms_pair_mean_vec_kernel(const float* __restrict__ a, int a_spli
     }
 }
 
+// y = o * rsqrt(mean over the whole row of o^2 + eps) * w * gate(g), gate 0: silu, 1: sigmoid; a block per row
+template <typename TG, typename TO>
+__global__ void rms_gate_kernel(const float* __restrict__ o, const float* __restrict__ w, float eps, const TG* __restrict__ g,
+                                long long g_stride, int gate, TO* __restrict__ out, int W) {
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t row = (size_t)blockIdx.x * W;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) { const float x = o[row + i]; ss += x * x; }
+    const float inv = rsqrtf(block_sum_any(ss, scratch) / (float)W + eps);
+    const TG* gr = g + (size_t)blockIdx.x * g_stride;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        const float z = to_float<TG>(gr[i]), s = 1.0f / (1.0f + expf(-z));
+        out[row + i] = from_float<TO>(o[row + i] * inv * w[i] * (gate ? s : z * s));
+    }
+}
+
 }  // namespace
+
+// o [T, W] float32 -> out [T, W]: the RMS norm over the whole row with the weight w, times silu (gate 0) or sigmoid (gate 1)
+// of g, whose rows are g_stride elements apart.
+PH_EXPORT int ph_rms_gate(const float* o, const float* w, float eps, const void* g, int g_dtype, long long g_stride, int gate, void* out,
+                          int out_dtype, int T, int W, cudaStream_t stream) {
+    if (!o || !w || !g || !out || T < 0 || W < 1 || gate < 0 || gate > 1 || !valid_dtype(g_dtype) || !valid_dtype(out_dtype))
+        return fail(PH_ERR_ARG, "rms_gate: bad arguments (T %d, W %d)", T, W);
+    if (T == 0) return PH_OK;
+    int threads = (W / 4 + 31) / 32 * 32;
+    threads = threads < 64 ? 64 : threads > 512 ? 512 : threads;
+    PH_DISPATCH(g_dtype, TG, PH_DISPATCH(out_dtype, TO,
+        launch_overlapped(rms_gate_kernel<TG, TO>, dim3(T), dim3(threads), 0, stream, o, w, eps, (const TG*)g, g_stride, gate, (TO*)out, W)));
+    return check_launch("rms_gate");
+}
 
 // A request's state is [H][DV][padded D] float32, padded D = 16 times the power of two that holds D / 16 (the kernel's
 // threads own 16 key channels each); slot_stride is its size.
+// head_decay ([H], or null): every key channel of head h decays by head_decay[h] at every token, and z is not read.
+// in_act 1: q, k and v pass through silu first.  raw_only 1: o is left in `raw` (float32) and neither normed nor gated.
 // chunks (n_chunks > 0): the step's rows cut into chunks per request ([n][4]: first row, rows, segment, last flag) with
 // seg_chunks [S + 1], carry [n_chunks, H, DV, padded D] and decay [n_chunks, H, D] as scratch: the chunks' own sums side by side,
 // a carry pass over each request's chunks, then the outputs chunk by chunk.  Without chunks a block walks a whole portion.
@@ -390,9 +436,10 @@ PH_EXPORT int ph_decayed_scan(const void* q, const void* k, const void* v, const
                               long long z_stride, const float* z_bias, float tau, float q_scale, const float* norm_w, float eps,
                               float* state, long long slot_stride, const int32_t* seg_start, const int32_t* seg_slot, int S, int T, int H,
                               int D, int DV, const int32_t* chunks, int n_chunks, const int32_t* seg_chunks, float* carry, float* decay,
-                              float* raw, void* out, cudaStream_t stream) {
-    if (!q || !k || !v || !g || !z || !norm_w || !state || !seg_start || !seg_slot || !raw || !out || S < 0 || T < 0 || H < 1 || D < 1 ||
-        DV < 1 || !(tau > 0.0f) || !valid_dtype(dtype) || n_chunks < 0 || (n_chunks && (!chunks || !seg_chunks || !carry || !decay)))
+                              float* raw, void* out, const float* head_decay, int in_act, int raw_only, cudaStream_t stream) {
+    if (!q || !k || !v || !state || !seg_start || !seg_slot || !raw || S < 0 || T < 0 || H < 1 || D < 1 ||
+        DV < 1 || !(tau > 0.0f) || !valid_dtype(dtype) || n_chunks < 0 || (n_chunks && (!chunks || !seg_chunks || !carry || !decay)) ||
+        (!z && !head_decay) || (!raw_only && (!g || !norm_w || !out)))
         return fail(PH_ERR_ARG, "decayed_scan: bad arguments (S %d, H %d, D %d, DV %d)", S, H, D, DV);
     if (S == 0 || T == 0) return PH_OK;
     int parts = 1;
@@ -414,8 +461,9 @@ PH_EXPORT int ph_decayed_scan(const void* q, const void* k, const void* v, const
     p.inv_tau = 1.0f / tau; p.q_scale = q_scale; p.eps = eps; p.norm_w = norm_w; p.state = state; p.slot_stride = slot_stride;
     p.seg_start = seg_start; p.seg_slot = seg_slot; p.chunks = chunks; p.seg_chunks = seg_chunks; p.carry = carry; p.decay = decay;
     p.raw = raw; p.out = out; p.H = H; p.D = D; p.DV = DV; p.parts = parts; p.cols = cols; p.tile = tile;
+    p.head_decay = head_decay; p.in_act = in_act ? 1 : 0;
     const int col_tiles = (DV + cols - 1) / cols;
-    p.fused_norm = col_tiles == 1;
+    p.fused_norm = col_tiles == 1 && !raw_only;
     const size_t smem = (size_t)(2 * tile * 3 * parts * SLICE + 2 * tile * cols) * sizeof(float);
 #define LAUNCH_SCAN(TX, MODE, ITEMS)                                                                                             \
     do {                                                                                                                         \
@@ -432,7 +480,7 @@ PH_EXPORT int ph_decayed_scan(const void* q, const void* k, const void* v, const
         PH_DISPATCH(dtype, TX, LAUNCH_SCAN(TX, 2, n_chunks));
     }
 #undef LAUNCH_SCAN
-    if (!p.fused_norm) {
+    if (!p.fused_norm && !raw_only) {
         const long long items = (long long)T * H;
         PH_DISPATCH(dtype, TX, launch_overlapped(head_norm_gate_kernel<TX>, dim3((unsigned)((items + 3) / 4)), dim3(128), 0, stream, p, T));
     }

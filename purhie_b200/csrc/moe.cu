@@ -16,7 +16,8 @@
 //                  that feature's weight row once, 16 bytes per lane and load, for up to eight rows of the tile at a
 //                  time; a row's sum is taken in one order (lane by lane over k, then a butterfly), whatever else
 //                  the tile holds.  This is weight streaming: its bound is the bytes of the chosen experts.
-//   route_combine  out[t] = base[t] (optional: float32 partial sums of a part that runs for every token) + the sum over the
+//   route_combine  out[t] = base[t] (optional: float32 partial sums of a part that runs for every token, times base_scale[t]
+//                  where a factor per token is given) + the sum over the
 //                  token's choices, in the order of the choices, of weight * y[position of (t, j)].
 #include "common.cuh"
 
@@ -37,7 +38,9 @@ template <typename TX, int TOK>
 __global__ void __launch_bounds__(RT_WARPS * 32) route_kernel(const TX* __restrict__ x, const float* __restrict__ w,
                                                               const float* __restrict__ bias, int T, int E, int K, int top,
                                                               int32_t* __restrict__ choice, float* __restrict__ weight, int scoring,
-                                                              const float* __restrict__ correction, int groups, int keep) {
+                                                              const float* __restrict__ correction, int groups, int keep,
+                                                              float weight_scale, const float* __restrict__ gate_w,
+                                                              float* __restrict__ gate_out) {
     __shared__ float logit[TOK][MAX_EXPERTS / TOK];             // what the choice goes by
     __shared__ float score[TOK][MAX_EXPERTS / TOK];             // scoring 1: sigmoid(logit), what the weights are
     __shared__ float run_rank[TOK][MAX_EXPERTS / TOK];
@@ -50,8 +53,9 @@ __global__ void __launch_bounds__(RT_WARPS * 32) route_kernel(const TX* __restri
     const TX* xr[TOK];
 #pragma unroll
     for (int i = 0; i < TOK; ++i) xr[i] = x + (size_t)(t0 + i < T ? t0 + i : t0) * K;
-    for (int e = warp; e < E; e += RT_WARPS) {
-        const float* wr = w + (size_t)e * K;
+    // one more row when a gate per token is asked for: gate_out[t] = sigmoid(gate_w . x[t])
+    for (int e = warp; e < E + (gate_w ? 1 : 0); e += RT_WARPS) {
+        const float* wr = e < E ? w + (size_t)e * K : gate_w;
         float acc[TOK];
 #pragma unroll
         for (int i = 0; i < TOK; ++i) acc[i] = 0.0f;
@@ -82,7 +86,9 @@ __global__ void __launch_bounds__(RT_WARPS * 32) route_kernel(const TX* __restri
 #pragma unroll
         for (int i = 0; i < TOK; ++i) {
             const float total = warp_sum(acc[i]);
-            if (lane == 0) {
+            if (lane == 0 && e == E) {
+                if (t0 + i < T) gate_out[t0 + i] = 1.0f / (1.0f + expf(-total));
+            } else if (lane == 0) {
                 float z = total + (bias ? bias[e] : 0.0f);
                 if (scoring == 1) {
                     z = 1.0f / (1.0f + expf(-z));
@@ -97,6 +103,17 @@ __global__ void __launch_bounds__(RT_WARPS * 32) route_kernel(const TX* __restri
     __syncthreads();
     if (warp >= TOK || t0 + warp >= T) return;                 // one warp per token picks
     const int t = t0 + warp;
+    if (scoring == 2) {
+        // the softmax over all experts: what the choice goes by and what the weights are made of
+        float largest = -INFINITY;
+        for (int e = lane; e < E; e += 32) largest = fmaxf(largest, logit[warp][e]);
+        largest = warp_max(largest);
+        float sum = 0.0f;
+        for (int e = lane; e < E; e += 32) { const float x = expf(logit[warp][e] - largest); logit[warp][e] = x; sum += x; }
+        sum = warp_sum(sum);
+        for (int e = lane; e < E; e += 32) logit[warp][e] = logit[warp][e] / sum;
+        __syncwarp();
+    }
     if (groups > 1 && keep < groups) {
         const int per = E / groups;
         for (int g = lane; g < groups; g += 32) {
@@ -106,7 +123,7 @@ __global__ void __launch_bounds__(RT_WARPS * 32) route_kernel(const TX* __restri
                 if (v > first) { second = first; first = v; }
                 else if (v > second) second = v;
             }
-            run_rank[warp][g] = per > 1 ? first + second : first;
+            run_rank[warp][g] = (per > 1 && scoring != 2) ? first + second : first;      // scoring 2: a run counts as its best
         }
         __syncwarp();
         for (int g = lane; g < groups; g += 32) {
@@ -145,6 +162,13 @@ __global__ void __launch_bounds__(RT_WARPS * 32) route_kernel(const TX* __restri
     }
     if (scoring == 1) {
         if (lane < top) weight[(size_t)t * top + lane] = score[warp][picked_index[warp][lane]];
+        return;
+    }
+    if (scoring == 2) {
+        // the chosen scores over their sum (added in the order of the choices), times the scale
+        float sum = 0.0f;
+        for (int j = 0; j < top; ++j) sum += picked_value[warp][j];
+        for (int j = lane; j < top; j += 32) weight[(size_t)t * top + j] = picked_value[warp][j] / (sum + 1e-20f) * weight_scale;
         return;
     }
     const float largest = picked_value[warp][0];
@@ -343,15 +367,17 @@ __global__ void route_gather_vec_kernel(const TX* __restrict__ x, const int32_t*
 template <typename TY>
 __global__ void route_combine_kernel(const TY* __restrict__ y, const int32_t* __restrict__ position, const float* __restrict__ weight,
                                      int top, float* __restrict__ out, int E_out, long long total, const float* __restrict__ base,
-                                     int base_splits, long long base_stride) {
+                                     int base_splits, long long base_stride, const float* __restrict__ base_scale) {
     pdl_launch_dependents();
     pdl_wait();
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     const int t = (int)(idx / E_out), c = (int)(idx % E_out);
     float acc = 0.0f;
-    if (base)
+    if (base) {
         for (int s = 0; s < base_splits; ++s) acc += base[(size_t)s * base_stride + idx];
+        if (base_scale) acc *= base_scale[t];
+    }
     for (int j = 0; j < top; ++j)
         acc += weight[(size_t)t * top + j] * to_float<TY>(y[(size_t)position[(size_t)t * top + j] * E_out + c]);
     out[idx] = acc;
@@ -360,7 +386,7 @@ __global__ void route_combine_kernel(const TY* __restrict__ y, const int32_t* __
 // float32 y, four columns per thread
 __global__ void route_combine_vec_kernel(const float* __restrict__ y, const int32_t* __restrict__ position, const float* __restrict__ weight,
                                          int top, float* __restrict__ out, int E_out, long long total4, const float* __restrict__ base,
-                                         int base_splits, long long base_stride) {
+                                         int base_splits, long long base_stride, const float* __restrict__ base_scale) {
     pdl_launch_dependents();
     pdl_wait();
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -373,6 +399,7 @@ __global__ void route_combine_vec_kernel(const float* __restrict__ y, const int3
             const float4 v = *reinterpret_cast<const float4*>(base + (size_t)s * base_stride + (size_t)t * E_out + c);
             acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
         }
+    if (base && base_scale) { const float f = base_scale[t]; acc.x *= f; acc.y *= f; acc.z *= f; acc.w *= f; }
     for (int j = 0; j < top; ++j) {
         const float wj = weight[(size_t)t * top + j];
         const float4 v = *reinterpret_cast<const float4*>(y + (size_t)position[(size_t)t * top + j] * E_out + c);
@@ -386,11 +413,14 @@ __global__ void route_combine_vec_kernel(const float* __restrict__ y, const int3
 // x [T, K] (the model's dtype), w [E, K] float32, bias [E] or null -> choice [T, top], weight [T, top].
 // scoring 0: softmax over the chosen logits; 1: sigmoid scores, the choice by score + correction (null: none), within the
 // `keep` best of `groups` runs of neighbouring experts (groups 1: no runs).
+// scoring 2: scores are the softmax over all experts; a run counts as its largest score; the weights are the chosen scores over
+// their sum (+ 1e-20), times weight_scale.  gate_w ([K] float32, or null) with gate_out [T]: sigmoid(gate_w . x) per token.
 PH_EXPORT int ph_route(const void* x, int x_dtype, const float* w, const float* bias, int T, int E, int K, int top, int32_t* choice,
-                       float* weight, int scoring, const float* correction, int groups, int keep, cudaStream_t stream) {
+                       float* weight, int scoring, const float* correction, int groups, int keep, float weight_scale,
+                       const float* gate_w, float* gate_out, cudaStream_t stream) {
     if (!x || !w || !choice || !weight || T < 0 || E < 1 || K < 1 || top < 1 || top > E || !valid_dtype(x_dtype))
         return fail(PH_ERR_ARG, "route: bad arguments (T %d, experts %d, K %d, top %d)", T, E, K, top);
-    if (scoring < 0 || scoring > 1 || groups < 1 || E % groups || keep < 1 || keep > groups || (long long)keep * (E / groups) < top)
+    if (scoring < 0 || scoring > 2 || (gate_w && !gate_out) || groups < 1 || E % groups || keep < 1 || keep > groups || (long long)keep * (E / groups) < top)
         return fail(PH_ERR_ARG, "route: scoring %d with %d of %d runs of %d experts cannot give %d choices", scoring, keep, groups,
                     E / (groups > 0 ? groups : 1), top);
     if (top > MAX_TOP || E > MAX_EXPERTS)
@@ -400,10 +430,11 @@ PH_EXPORT int ph_route(const void* x, int x_dtype, const float* w, const float* 
     if (!aligned) return fail(PH_ERR_ARG, "route: the rows must be 16-byte aligned");
     if (T >= 64 && E <= MAX_EXPERTS / 4)
         PH_DISPATCH(x_dtype, TX, launch_overlapped(route_kernel<TX, 4>, dim3((T + 3) / 4), dim3(RT_WARPS * 32), 0, stream, (const TX*)x, w,
-                                                   bias, T, E, K, top, choice, weight, scoring, correction, groups, keep));
+                                                   bias, T, E, K, top, choice, weight, scoring, correction, groups, keep, weight_scale, gate_w,
+                                                   gate_out));
     else
         PH_DISPATCH(x_dtype, TX, launch_overlapped(route_kernel<TX, 1>, dim3(T), dim3(RT_WARPS * 32), 0, stream, (const TX*)x, w, bias, T,
-                                                   E, K, top, choice, weight, scoring, correction, groups, keep));
+                                                   E, K, top, choice, weight, scoring, correction, groups, keep, weight_scale, gate_w, gate_out));
     return check_launch("route");
 }
 
@@ -475,17 +506,18 @@ PH_EXPORT int ph_gemv_grouped(const void* x, int x_dtype, const int32_t* pair_at
 }
 
 PH_EXPORT int ph_route_combine(const void* y, int y_dtype, const int32_t* position, const float* weight, int T, int top, int E_out,
-                               float* out, const float* base, int base_splits, long long base_stride, cudaStream_t stream) {
+                               float* out, const float* base, int base_splits, long long base_stride, const float* base_scale,
+                               cudaStream_t stream) {
     if (!y || !position || !weight || !out || T < 0 || top < 1 || E_out < 1 || !valid_dtype(y_dtype) || (base && base_splits < 1))
         return fail(PH_ERR_ARG, "route_combine: bad arguments (T %d, top %d, width %d)", T, top, E_out);
     const long long total = (long long)T * E_out;
     if (total == 0) return PH_OK;
     if (y_dtype == PH_F32 && E_out % 4 == 0 && (((uintptr_t)y | (uintptr_t)out | (uintptr_t)base) & 15) == 0 && base_stride % 4 == 0) {
         launch_overlapped(route_combine_vec_kernel, dim3((unsigned)((total / 4 + 255) / 256)), dim3(256), 0, stream, (const float*)y, position,
-                          weight, top, out, E_out, total / 4, base, base_splits, base_stride);
+                          weight, top, out, E_out, total / 4, base, base_splits, base_stride, base_scale);
         return check_launch("route_combine");
     }
     PH_DISPATCH(y_dtype, TY, launch_overlapped(route_combine_kernel<TY>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream,
-                                               (const TY*)y, position, weight, top, out, E_out, total, base, base_splits, base_stride));
+                                               (const TY*)y, position, weight, top, out, E_out, total, base, base_splits, base_stride, base_scale));
     return check_launch("route_combine");
 }

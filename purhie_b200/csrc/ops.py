@@ -105,7 +105,7 @@ _SIGNATURES = {
                                 c_void_p, c_int, c_void_p],
         "ph_attention_generic": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_longlong, c_int, c_void_p, c_int,
                                  c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
-                                 c_int, c_int, c_void_p],
+                                 c_int, c_int, c_int, c_void_p],
         "ph_gemm_simple": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "ph_argmax": [c_void_p, c_int, c_int, c_void_p, c_void_p],
         "ph_argmax_parts": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_longlong, c_void_p],
@@ -281,7 +281,7 @@ def qk_norm_rope_kv_write(qkv: torch.Tensor, q_out: torch.Tensor, positions: tor
 def attention_generic(q: torch.Tensor, k_base: torch.Tensor, v_base: torch.Tensor, page_stride: int, page_size: int,
                       block_table: torch.Tensor, row_seg: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, *,
                       num_heads: int, num_kv_heads: int, head_dim: int, window: Optional[int], scale: float,
-                      value_dim: int = 0, chunk: int = 0) -> torch.Tensor:
+                      value_dim: int = 0, chunk: int = 0, value_stride: int = 0) -> torch.Tensor:
     _need(q, "q"); _need(k_base, "k_base"); _need(v_base, "v_base"); _need(out, "out")
     _need(block_table, "block_table", torch.int32); _need(row_seg, "row_seg", torch.int32)
     _need(positions, "positions", torch.int32)
@@ -293,7 +293,7 @@ def attention_generic(q: torch.Tensor, k_base: torch.Tensor, v_base: torch.Tenso
     call("core", "ph_attention_generic", _ptr(q), _code(q.dtype), _ptr(k_base), _ptr(v_base), _code(k_base.dtype),
          page_stride, page_size, _ptr(block_table), block_table.shape[-1], _ptr(row_seg), _ptr(positions), _ptr(out),
          _code(out.dtype), T, num_heads, num_kv_heads, head_dim, int(window or 0), float(scale), int(value_dim), int(chunk),
-         _stream())
+         int(value_stride), _stream())
     return out
 
 

@@ -281,6 +281,20 @@ Tensor Engine::forward(StepContext& ctx, const int32_t* want_rows, int n_want) {
             }
             for (size_t i = 0; i < (size_t)T * E; i++) x[i] += tr.factor * add[i];
         }
+        if (stream.has_also) {                                    // the second addend of a layer whose parts read the same rows
+            const Tensor& p = stream.also.tensor;
+            const size_t n = (size_t)stream.also.splits * T * E;
+            std::vector<uint8_t> raw(n * dtype_size(p.dtype));
+            QE_CUDA(cudaMemcpy(raw.data(), p.data, raw.size(), cudaMemcpyDeviceToHost));
+            for (int s = 0; s < stream.also.splits; s++)
+                for (size_t i = 0; i < (size_t)T * E; i++) {
+                    const size_t j = (size_t)s * T * E + i;
+                    float v;
+                    if (p.dtype == DType::F32) memcpy(&v, raw.data() + 4 * j, 4);
+                    else { uint16_t h; memcpy(&h, raw.data() + 2 * j, 2); v = bf16_to_f32(h); }
+                    x[i] += v;
+                }
+        }
         layer_dump_(entry, x.data(), T, E);
     };
     return model_->forward(ctx, views_, want_rows, n_want, dump);

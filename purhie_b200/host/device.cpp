@@ -171,6 +171,12 @@ const CoreKernels& core_kernels() {
     bind(h, "core", "ph_gemv_grouped", g_core.gemv_grouped);
     bind(h, "core", "ph_route_gather", g_core.route_gather);
     bind(h, "core", "ph_route_combine", g_core.route_combine);
+    bind(h, "core", "ph_rms_gate", g_core.rms_gate);
+    bind(h, "core", "ph_add_dyntanh", g_core.add_dyntanh);
+    bind(h, "core", "ph_concat_restart", g_core.concat_restart);
+    bind(h, "core", "ph_latent_prepare", g_core.latent_prepare);
+    bind(h, "core", "ph_latent_absorb", g_core.latent_absorb);
+    bind(h, "core", "ph_latent_expand", g_core.latent_expand);
     bind(h, "core", "ph_core_last_error", g_core.last_error);
     g_core_ok = true;
     return g_core;

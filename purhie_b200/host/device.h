@@ -99,7 +99,7 @@ struct CoreKernels {
                                  const float*, int, cudaStream_t);
     int (*add_weight_sumsq)(float*, const void*, int, int, long long, const float*, int, int, void*, int, float*, int, cudaStream_t);
     int (*attention_generic)(const void*, int, const void*, const void*, int, long long, int, const int32_t*, int,
-                             const int32_t*, const int32_t*, void*, int, int, int, int, int, int, float, int, int, cudaStream_t);
+                             const int32_t*, const int32_t*, void*, int, int, int, int, int, int, float, int, int, int, cudaStream_t);
     int (*gemm_simple)(const void*, int, const void*, int, void*, int, int, int, int, cudaStream_t);
     int (*argmax)(const float*, int, int, int32_t*, void*, long long, cudaStream_t);   // several CTAs per row, with scratch
     long long (*argmax_scratch_bytes)(int);
@@ -119,7 +119,9 @@ struct CoreKernels {
     // outputs, each RMS-normed over the width, combined
     int (*decayed_scan)(const void*, const void*, const void*, const void*, int, long long, const float*, long long, const float*, float,
                         float, const float*, float, float*, long long, const int32_t*, const int32_t*, int, int, int, int, int,
-                        const int32_t*, int, const int32_t*, float*, float*, float*, void*, cudaStream_t);
+                        const int32_t*, int, const int32_t*, float*, float*, float*, void*, const float*, int, int, cudaStream_t);
+    // a float32 row RMS-normed over its whole width, times silu or sigmoid of a gate
+    int (*rms_gate)(const float*, const float*, float, const void*, int, long long, int, void*, int, int, int, cudaStream_t);
     int (*rms_pair_mean)(const void*, int, int, long long, const float*, const void*, int, int, long long, const float*, float, float,
                          float*, int, int, cudaStream_t);
     // selective state-space mixer: convolution + silu, and the scan
@@ -131,7 +133,7 @@ struct CoreKernels {
     // routing: router logits and top-k (softmax over the chosen, or sigmoid scores with a correction and runs of experts),
     // sort by expert, products by expert, weighted sum (on top of a base addend)
     int (*route)(const void*, int, const float*, const float*, int, int, int, int, int32_t*, float*, int, const float*, int, int,
-                 cudaStream_t);
+                 float, const float*, float*, cudaStream_t);
     int (*route_max_tiles)(int, int);
     int (*route_sort)(const int32_t*, int, int, int32_t*, int32_t*, int32_t*, int, int32_t*, cudaStream_t);
     int (*gemm_grouped)(const void*, int, const int32_t*, int, const void*, int, const int32_t*, int, void*, int, int, int,
@@ -139,7 +141,19 @@ struct CoreKernels {
     int (*gemv_grouped)(const void*, int, const int32_t*, int, const void*, int, const int32_t*, int, void*, int, int, int,
                         cudaStream_t);
     int (*route_gather)(const void*, int, const int32_t*, int, void*, int, int, cudaStream_t);
-    int (*route_combine)(const void*, int, const int32_t*, const float*, int, int, int, float*, const float*, int, long long, cudaStream_t);
+    int (*route_combine)(const void*, int, const int32_t*, const float*, int, int, int, float*, const float*, int, long long, const float*,
+                         cudaStream_t);
+    // dynamic tanh with the residual add (two addends) in front; the stream re-started from [x | what the embedding gave]
+    int (*add_dyntanh)(float*, const void*, int, int, long long, const void*, int, int, long long, const float*, const float*, const float*,
+                       const int32_t*, int, int, void*, int, int, cudaStream_t);
+    int (*concat_restart)(float*, const void*, int, int, long long, const void*, int, int, long long, const float*, const float*, void*, int,
+                          int, int, cudaStream_t);
+    // attention through a latent: norms, rotation and the cache row; the key expansion folded into q; the value expansion
+    int (*latent_prepare)(const void*, int, long long, int, int, int, const float*, const float*, float, const float*, int, int,
+                          const int32_t*, const int32_t*, void*, int, void*, int, long long, int, int, cudaStream_t);
+    int (*latent_absorb)(const void*, int, const void*, int, const float*, int, int, const int32_t*, void*, int, int, int, int, int, int,
+                         cudaStream_t);
+    int (*latent_expand)(const void*, int, const void*, int, const void*, int, long long, void*, int, int, int, int, int, cudaStream_t);
     const char* (*last_error)(void);
 };
 struct FlashKernels {

@@ -319,7 +319,7 @@ public:
         } else {
             QE_LAUNCH(core, core.attention_generic(q.data, q.code(), cache.k_base, cache.v_base, (int)cache.kv_dtype, cache.page_stride,
                                                    cache.page_size, g.block_table, g.table_width, ctx.row_seg, abs_positions, out.data,
-                                                   out.code(), T, heads_, kv_heads_, head_dim_, window_, (float)scale_, value_dim_, chunk_,
+                                                   out.code(), T, heads_, kv_heads_, head_dim_, window_, (float)scale_, value_dim_, chunk_, 0,
                                                    ctx.stream));
         }
         return o_proj_(out, ctx, "o_out", DType::F32, T, true, false, ctx.residual, nullptr, &ctx.norm_ahead);

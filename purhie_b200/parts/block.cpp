@@ -10,6 +10,16 @@
 // the pass in which it adds and norms, so a layer still launches two norm kernels.  Sub-parts by name: mixer_norm,
 // mixer, mixer_post_norm, and, unless the layer has no feed-forward, feed_forward_norm, feed_forward,
 // feed_forward_post_norm.
+//
+// parallel: h = norm(x); x += mixer(h) + feed_forward(h): one norm, and both parts read what it gives (the feed-forward is
+// optional).  The two addends wait side by side in the stream and the next norm folds both in its one pass.  Sub-parts
+// by name: norm, mixer, feed_forward.
+//
+// reinject: x <- W [x ; e] + step[pass], e the rows the embedding gave (the model keeps them: ModelSpec::
+// keep_embedding_output), W [E, 2E], step [passes, E] and pass the run-order entry's LayerCall::pass.  It has no mixer,
+// keeps nothing in the cache, and stands in the run order in front of each round of a stretch of layers that runs
+// several times.  Layer params: hidden_size, passes, names{weight, step}.
+#include "linear.h"
 #include "parts.h"
 
 namespace qe {
@@ -103,10 +113,103 @@ private:
     std::shared_ptr<FeedForward> ff_;
 };
 
+class ParallelBlock : public Arrangement {
+public:
+    ParallelBlock(const LayerSpec& layer, BuildContext& build) {
+        norm_ = make_part_as<Norm>("norm", layer.part("norm"), build);
+        mixer_ = make_part_as<Mixer>("mixer", layer.part("mixer"), build);
+        if (layer.has("feed_forward")) ff_ = make_part_as<FeedForward>("feed_forward", layer.part("feed_forward"), build);
+    }
+    std::vector<Part*> parts() override {
+        std::vector<Part*> p = {norm_.get(), mixer_.get()};
+        if (ff_) p.push_back(ff_.get());
+        return p;
+    }
+    CacheNeed cache_need() const override { return mixer_->cache_need(); }
+    void forward(ResidualStream& stream, StepContext& ctx, const CacheView& cache) override {
+        // both parts read the same finished rows; a product may add into the residual itself (the rows are made by then),
+        // but no norm's work is handed to it: the rows behind this layer are the sum of two addends
+        ctx.row_scale = RowScale();
+        ctx.norm_ahead = NormAhead();
+        Tensor h = norm_->forward(stream, ctx);
+        ctx.residual = stream.x.as<float>();
+        ctx.residual_width = stream.x.shape[1];
+        stream.add(mixer_->forward(h, ctx, cache));
+        if (ff_) {
+            Addend fed = ff_->forward(h, ctx);
+            if (stream.has_pending) stream.add_also(std::move(fed));
+            else stream.add(std::move(fed));
+        }
+    }
+private:
+    std::shared_ptr<Norm> norm_;
+    std::shared_ptr<Mixer> mixer_;
+    std::shared_ptr<FeedForward> ff_;
+};
+
+// The weights of a reinjection, as a part so that the loader, the folder check and random weights see them.
+class ReinjectWeights : public Part {
+public:
+    ReinjectWeights(const Json& p, BuildContext& b)
+        : Part(p, b), hidden_(p.at("hidden_size").as_int()), passes_(p.at("passes").as_int()), gemm_(b.options.get_string("gemm", "auto")) {
+        if (hidden_ < 1 || passes_ < 1) throw ConfigError("reinject: hidden_size and passes must be positive");
+    }
+    std::vector<TensorSpec> tensor_specs() const override {
+        return {{name_of("weight"), {hidden_, 2 * hidden_}, Role::Matrix, Init::Normal}, {name_of("step"), {passes_, hidden_}, Role::Vector, Init::Normal}};
+    }
+    void bind(WeightSource& src) override {
+        proj = Linear(src.fetch(name_of("weight")), "reinject", gemm_);
+        step = src.fetch(name_of("step"));
+    }
+    std::vector<std::string> required_libraries() const override { return proj.defined() ? proj.required_libraries() : std::vector<std::string>{"core"}; }
+    int64_t hidden_, passes_;
+    std::string gemm_;
+    Linear proj;
+    Tensor step;
+};
+
+class ReinjectBlock : public Arrangement {
+public:
+    ReinjectBlock(const LayerSpec& layer, BuildContext& build) : weights_(std::make_shared<ReinjectWeights>(layer.params, build)) {}
+    std::vector<Part*> parts() override { return {weights_.get()}; }
+    CacheNeed cache_need() const override { return CacheNeed(); }
+    void forward(ResidualStream& stream, StepContext& ctx, const CacheView&) override {
+        if (!ctx.embedding_output) throw Error(kInvalidState, "reinject: the model does not keep what the embedding gave");
+        if (ctx.pass < 0 || ctx.pass >= weights_->passes_) throw Error(kInvalidState, "reinject: pass " + std::to_string(ctx.pass) + " of " + std::to_string(weights_->passes_));
+        const int64_t E = weights_->hidden_;
+        if (stream.has_pending && stream.pending.transform.defined()) fold_all_addends(stream, ctx);
+        const DType dt = weights_->compute_dtype;
+        Tensor cat = ctx.workspace->get("reinject_rows", {ctx.T, 2 * E}, dt);
+        const CoreKernels& k = core_kernels();
+        const Addend* a = stream.has_pending ? &stream.pending : nullptr;
+        const Addend* b = stream.has_also ? &stream.also : nullptr;
+        if (LaunchProfile::get().on()) {
+            double bytes = (double)ctx.T * E * (12.0 + 2.0 * dtype_size(dt));
+            if (a) bytes += (double)a->splits * ctx.T * E * dtype_size(a->tensor.dtype);
+            if (b) bytes += (double)b->splits * ctx.T * E * dtype_size(b->tensor.dtype);
+            LaunchProfile::get().note_cost(bytes, 0.0);
+        }
+        // cat = [x + what waits | e]; x restarts as the pass's step vector, and the product over cat is added to it
+        QE_LAUNCH(k, k.concat_restart(stream.x.as<float>(), a ? a->tensor.data : nullptr, a ? a->tensor.code() : 0, a ? a->splits : 1,
+                                      a ? (long long)ctx.T * E : 0, b ? b->tensor.data : nullptr, b ? b->tensor.code() : 0, b ? b->splits : 1,
+                                      b ? (long long)ctx.T * E : 0, ctx.embedding_output, weights_->step.as<float>() + (size_t)ctx.pass * E,
+                                      cat.data, cat.code(), ctx.T, (int)E, ctx.stream));
+        stream.clear();
+        ctx.residual = stream.x.as<float>();
+        ctx.residual_width = E;
+        ctx.row_scale = RowScale();
+        ctx.norm_ahead = NormAhead();
+        stream.add(weights_->proj(cat, ctx, "reinject_out", DType::F32, ctx.T, true, false, ctx.residual));
+    }
+private:
+    std::shared_ptr<ReinjectWeights> weights_;
+};
+
 void register_norm_parts();
 void register_routed_parts();
 void register_state_space_parts();
 void register_linear_attention_parts();
+void register_latent_attention_parts();
 void register_position_parts();
 void register_mixer_parts();
 void register_feed_forward_parts();
@@ -124,8 +227,15 @@ void register_builtin_parts() {
     register_routed_parts();
     register_state_space_parts();
     register_linear_attention_parts();
+    register_latent_attention_parts();
     register_arrangement("sandwich_norm", [](const LayerSpec& layer, BuildContext& build) {
         return std::unique_ptr<Arrangement>(new SandwichNormBlock(layer, build));
+    });
+    register_arrangement("parallel", [](const LayerSpec& layer, BuildContext& build) {
+        return std::unique_ptr<Arrangement>(new ParallelBlock(layer, build));
+    });
+    register_arrangement("reinject", [](const LayerSpec& layer, BuildContext& build) {
+        return std::unique_ptr<Arrangement>(new ReinjectBlock(layer, build));
     });
     register_arrangement("pre_norm", [](const LayerSpec& layer, BuildContext& build) {
         return std::unique_ptr<Arrangement>(new PreNormBlock(layer, build));

@@ -8,13 +8,21 @@
 
 namespace qe {
 
-// params: vocab_size, hidden_size, scale (default 1), names{weight}.
+// params: vocab_size, hidden_size, scale (default 1), norm (null, or a norm as {kind, params} that the gathered rows pass
+// through, in float32 and in place, before they become the residual stream), names{weight}.
 class TokenEmbedding : public Embedding {
 public:
     TokenEmbedding(const Json& p, BuildContext& b)
-        : Embedding(p, b), vocab_(p.at("vocab_size").as_int()), hidden_(p.at("hidden_size").as_int()), scale_(p.get_double("scale", 1.0)) {}
+        : Embedding(p, b), vocab_(p.at("vocab_size").as_int()), hidden_(p.at("hidden_size").as_int()), scale_(p.get_double("scale", 1.0)) {
+        if (const Json* n = p.find("norm"))
+            if (!n->is_null()) norm_ = make_part_as<Norm>("norm", PartSpec::from_json(*n), b);
+    }
     std::vector<TensorSpec> tensor_specs() const override { return {{name_of("weight"), {vocab_, hidden_}, Role::Matrix, Init::Normal}}; }
-    void bind(WeightSource& src) override { table_ = src.fetch(name_of("weight")); }
+    void bind(WeightSource& src) override {
+        table_ = src.fetch(name_of("weight"));
+        if (norm_) norm_->bind(src);
+    }
+    std::vector<Part*> children() override { return norm_ ? std::vector<Part*>{norm_.get()} : std::vector<Part*>{}; }
     Tensor forward(StepContext& ctx) override {
         Tensor x = ctx.workspace->get("residual", {ctx.T, hidden_}, DType::F32);
         const CoreKernels& k = core_kernels();
@@ -23,12 +31,14 @@ public:
         else
             QE_LAUNCH(k, k.embed_gather_scaled(table_.data, table_.code(), ctx.token_ids, x.as<float>(), ctx.T, (int)hidden_, (int)vocab_,
                                                (float)scale_, ctx.stream));
+        if (norm_) norm_->apply_in_place(x, ctx, ctx.T);
         return x;
     }
 private:
     int64_t vocab_, hidden_;
     double scale_;
     Tensor table_;
+    std::shared_ptr<Norm> norm_;
 };
 
 // params: hidden_size, vocab_size, and either names{weight} or tied_to (a tensor another part reads); ignore: names

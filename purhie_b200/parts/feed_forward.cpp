@@ -1,5 +1,6 @@
 // Gated feed-forward: y = Wd act(Wg x, Wu x), with act(g, u) = silu(g) * u (SwiGLU) unless the part is given another
-// gate: "clamped_swish" is g' sigmoid(alpha g') (u' + shift) with g' = min(g, limit), u' = clamp(u, -limit, limit).
+// gate: "clamped_swish" is g' sigmoid(alpha g') (u' + shift) with g' = min(g, limit), u' = clamp(u, -limit, limit);
+// "gelu_tanh" is gelu(g) * u with the tanh form of gelu.
 //
 // A feed-forward without a gate ("mlp") is y = Wd act(Wu x).
 //
@@ -12,7 +13,7 @@
 namespace qe {
 
 // params: hidden_size, intermediate_size, activation (null: silu; or {"kind": "clamped_swish", "alpha", "limit",
-// "shift"}), names{gate_proj, up_proj, down_proj}.
+// "shift"}; or {"kind": "gelu_tanh"}), names{gate_proj, up_proj, down_proj}.
 class SwiGLU : public FeedForward {
 public:
     SwiGLU(const Json& p, BuildContext& b)
@@ -54,7 +55,8 @@ public:
     Addend forward(const Tensor& x, StepContext& ctx) override {
         const int T = ctx.T;
         // where the tensor-core product runs, its epilogue applies the gate (either family); else a kernel behind it does
-        const float gate_constants[3] = {gate_.alpha, gate_.limit, gate_.shift};
+        float gate_constants[4];
+        gate_.constants(gate_constants);
         Addend gu = gate_up_(x, ctx, "gate_up", compute_dtype, T, true, true, nullptr, &ctx.row_scale, nullptr,
                              gate_.kind ? gate_constants : nullptr);
         Tensor act;

@@ -39,7 +39,7 @@ public:
     // scale: the rows of x lack a factor per row (RowScale); only where applies_row_scale() is true, and then the
     // kernel's epilogue multiplies by it.  ahead (with add_into, for a part's last product): the norm that follows
     // the addition; where the kernel adds in its epilogue and can, it fills ahead->rows and ahead->scale (NormAhead).
-    // gate (with fuse_swiglu): three floats, alpha, limit and shift of the clamped swish gate (gate.h); null: silu.
+    // gate (with fuse_swiglu): four floats, alpha, limit, shift and the kind of the gate (GateSpec::constants); null: silu.
     Addend operator()(const Tensor& x, StepContext& ctx, const std::string& out_name, DType out_dtype, int rows,
                       bool allow_split = false, bool fuse_swiglu = false, float* add_into = nullptr,
                       const RowScale* scale = nullptr, NormAhead* ahead = nullptr, const float* gate = nullptr) const;

@@ -10,6 +10,12 @@
 // exponential), S, o, the head norm and the gate are float32 in every mode; the products follow the model's dtype,
 // the decay's second product writes float32.  q, k, v and g come from one product over the stacked matrices.
 //
+// lightning_attention: the same matrix state with one constant decay per head and no logits:
+//     q = silu(Wq h), k = silu(Wk h), v = silu(Wv h),   S <- decay[head] S + k v^T,   o = S^T q
+//     y = Wo (rmsnorm(o; over all heads' values as one row, a weight per element) * sigmoid(Wg h))
+// It shares the recurrence's kernel (the decay as a constant, the activations on the way in, o left raw) and the chunk
+// lists with gated_linear_attention; the norm over the whole row and the gate are a kernel behind it.
+//
 // side_by_side: y = factor * (rmsnorm(left(h); w_left) + rmsnorm(right(h); w_right)), both norms over the model
 // width.  "left" and "right" are mixers of any registered kind, given as {kind, params}; one of them may keep pages
 // and one a state (CacheNeed::both), and each finds what it keeps in the layer's cache view.
@@ -20,6 +26,29 @@
 #include "parts.h"
 
 namespace qe {
+
+// The chunk list of a step for the recurrence's kernel ("decayed.chunks", "decayed.seg_chunks"): every request's rows in
+// chunks of `chunk` tokens when the longest portion has `from` tokens or more.  Shared by the mixers that use the kernel.
+namespace {
+void add_scan_chunks(StepPlan& plan, int chunk, int from) {
+    if (plan.has("decayed.chunks")) return;
+    int longest = 0;
+    for (int n : plan.q_lens) longest = std::max(longest, n);
+    if (longest < from) return;
+    std::vector<int32_t> items, seg_items = {0};
+    int row = 0;
+    for (int s = 0; s < plan.S; s++) {
+        const int n = plan.q_lens[s];
+        for (int at = 0; at < n; at += chunk) {
+            items.push_back(row + at); items.push_back(std::min(chunk, n - at)); items.push_back(s); items.push_back(at + chunk >= n);
+        }
+        row += n;
+        seg_items.push_back((int32_t)(items.size() / 4));
+    }
+    plan.add("decayed.chunks", std::move(items));
+    plan.add("decayed.seg_chunks", std::move(seg_items));
+}
+}  // namespace
 
 // params: hidden_size, num_heads, head_dim, value_dim, decay_rank (null: the stored matrices' inner size), tau, norm_eps,
 // names{q_proj, k_proj, v_proj, g_proj, o_proj, norm, decay_down, decay_up, decay_bias}.
@@ -93,24 +122,7 @@ public:
     // A step with a long prompt portion cuts every request's rows into chunks for the recurrence (first row, rows, segment,
     // 1 on the request's last chunk) so that a prompt's tokens are spread over the device: the chunk list is this mixer's
     // own metadata, shared by all layers of its kind.
-    void prepare_step(StepPlan& plan) override {
-        if (plan.has("decayed.chunks")) return;
-        int longest = 0;
-        for (int n : plan.q_lens) longest = std::max(longest, n);
-        if (longest < kChunkFrom) return;
-        std::vector<int32_t> items, seg_items = {0};
-        int row = 0;
-        for (int s = 0; s < plan.S; s++) {
-            const int n = plan.q_lens[s];
-            for (int at = 0; at < n; at += kChunk) {
-                items.push_back(row + at); items.push_back(std::min(kChunk, n - at)); items.push_back(s); items.push_back(at + kChunk >= n);
-            }
-            row += n;
-            seg_items.push_back((int32_t)(items.size() / 4));
-        }
-        plan.add("decayed.chunks", std::move(items));
-        plan.add("decayed.seg_chunks", std::move(seg_items));
-    }
+    void prepare_step(StepPlan& plan) override { add_scan_chunks(plan, kChunk, kChunkFrom); }
 
     Addend forward(const Tensor& x, StepContext& ctx, const CacheView& cache) override {
         const int64_t per_slot = (int64_t)heads_ * padded_dim() * vdim_;
@@ -142,7 +154,7 @@ public:
                                     qkvg.code(), width, z.as<float>(), key_width_, decay_bias_.as<float>(), (float)tau_,
                                     (float)(1.0 / std::sqrt((double)dim_)), norm_.as<float>(), (float)eps_, cache.state.as<float>(), per_slot,
                                     ctx.seg_start, ctx.seg_slot, ctx.S, T, heads_, dim_, vdim_, n_chunks ? chunks.data : nullptr, n_chunks,
-                                    n_chunks ? seg_chunks.data : nullptr, carry, decay, raw.as<float>(), y.data, ctx.stream));
+                                    n_chunks ? seg_chunks.data : nullptr, carry, decay, raw.as<float>(), y.data, nullptr, 0, 0, ctx.stream));
         return o_proj_(y, ctx, "gla_out", DType::F32, T, true, false, ctx.residual, nullptr, &ctx.norm_ahead);
     }
 
@@ -155,6 +167,113 @@ private:
     std::string gemm_;
     Linear qkvg_proj_, decay_down_, decay_up_, o_proj_;
     Tensor decay_bias_, norm_;
+};
+
+// params: hidden_size, num_heads, head_dim, value_dim, decay [num_heads] (each in (0, 1]), norm_eps,
+// names{q_proj, k_proj, v_proj, g_proj, o_proj, norm}.
+class LightningAttention : public Mixer {
+public:
+    LightningAttention(const Json& p, BuildContext& b) : Mixer(p, b) {
+        hidden_ = p.at("hidden_size").as_int();
+        heads_ = (int)p.at("num_heads").as_int();
+        dim_ = (int)p.at("head_dim").as_int();
+        vdim_ = (int)p.at("value_dim").as_int();
+        eps_ = p.at("norm_eps").as_double();
+        if (heads_ < 1 || dim_ < 1 || vdim_ < 1) throw ConfigError("lightning_attention: heads, head_dim and value_dim must be positive");
+        const Json& d = p.at("decay");
+        if (!d.is_array() || (int)d.size() != heads_) throw ConfigError("lightning_attention: decay must list one number per head");
+        for (const Json& v : d.items()) {
+            const double a = v.as_double();
+            if (!(a > 0.0) || a > 1.0) throw ConfigError("lightning_attention: a decay must lie in (0, 1]");
+            decay_host_.push_back((float)a);
+        }
+        gemm_ = b.options.get_string("gemm", "auto");
+        key_width_ = (int64_t)heads_ * dim_;
+        value_width_ = (int64_t)heads_ * vdim_;
+    }
+    std::vector<TensorSpec> tensor_specs() const override {
+        return {{name_of("q_proj"), {key_width_, hidden_}, Role::Matrix, Init::Normal},
+                {name_of("k_proj"), {key_width_, hidden_}, Role::Matrix, Init::Normal},
+                {name_of("v_proj"), {value_width_, hidden_}, Role::Matrix, Init::Normal},
+                {name_of("g_proj"), {value_width_, hidden_}, Role::Matrix, Init::Normal},
+                {name_of("o_proj"), {hidden_, value_width_}, Role::Matrix, Init::Normal},
+                {name_of("norm"), {value_width_}, Role::Vector, Init::Scale}};
+    }
+    void bind(WeightSource& src) override {
+        // one matrix [q | k | v | g]: the four projections of h are one product (a layout choice only)
+        Tensor parts[4] = {src.fetch(name_of("q_proj")), src.fetch(name_of("k_proj")), src.fetch(name_of("v_proj")), src.fetch(name_of("g_proj"))};
+        for (Tensor& t : parts)
+            if (t.dtype != parts[0].dtype) throw WeightError("the projections of " + name_of("q_proj") + "'s mixer are stored in different precisions");
+        Tensor all = src.arena().alloc(parts[0].dtype, {2 * key_width_ + 2 * value_width_, hidden_});
+        size_t off = 0;
+        for (Tensor& t : parts) {
+            QE_CUDA(cudaMemcpyAsync(static_cast<char*>(all.data) + off, t.data, t.bytes(), cudaMemcpyDeviceToDevice, src.stream()));
+            off += t.bytes();
+        }
+        decay_ = src.arena().alloc(DType::F32, {heads_});
+        QE_CUDA(cudaMemcpyAsync(decay_.data, decay_host_.data(), decay_host_.size() * sizeof(float), cudaMemcpyHostToDevice, src.stream()));
+        QE_CUDA(cudaStreamSynchronize(src.stream()));
+        for (Tensor& t : parts) src.release(t);
+        qkvg_proj_ = Linear(all, "qkvg_proj", gemm_);
+        norm_ = src.fetch(name_of("norm"));
+        o_proj_ = Linear(src.fetch(name_of("o_proj")), "o_proj", gemm_);
+    }
+    std::vector<std::string> required_libraries() const override {
+        return (qkvg_proj_.fast() || o_proj_.fast()) ? std::vector<std::string>{"core", "gemm100"} : std::vector<std::string>{"core"};
+    }
+    int preferred_row_multiple() const override { return (qkvg_proj_.fast() || o_proj_.fast()) ? 256 : 0; }
+    int64_t padded_dim() const {
+        int64_t parts = 1;
+        while (parts * 16 < dim_) parts *= 2;
+        return parts * 16;
+    }
+    CacheNeed cache_need() const override { return CacheNeed::state({heads_, vdim_, padded_dim()}, DType::F32); }
+    void prepare_step(StepPlan& plan) override { add_scan_chunks(plan, kChunk, kChunkFrom); }
+
+    Addend forward(const Tensor& x, StepContext& ctx, const CacheView& cache) override {
+        const int64_t per_slot = (int64_t)heads_ * padded_dim() * vdim_;
+        if (!cache.state.defined() || cache.state.dtype != DType::F32 || cache.state.numel() != (int64_t)cache.state.shape[0] * per_slot)
+            throw Error(kInvalidState, "lightning_attention: the cache manager gave no state of this mixer's shape");
+        const int T = ctx.T;
+        const DType dt = compute_dtype;
+        Workspace& ws = *ctx.workspace;
+        const CoreKernels& k = core_kernels();
+        const int64_t width = 2 * key_width_ + 2 * value_width_;
+        Tensor qkvg = qkvg_proj_(x, ctx, "la_qkvg", dt, T).tensor;                         // [T, q | k | v | g]
+        Tensor raw = ws.get("la_o_raw", {T, value_width_}, DType::F32);
+        Tensor y = ws.get("la_o", {T, value_width_}, dt);
+        const size_t es = dtype_size(dt);
+        char* base = static_cast<char*>(qkvg.data);
+        const StepArray chunks = ctx.array("decayed.chunks"), seg_chunks = ctx.array("decayed.seg_chunks");
+        const int n_chunks = chunks.count / 4;
+        float *carry = nullptr, *decay = nullptr;
+        if (n_chunks) {
+            carry = ws.get("la_carry", {n_chunks, heads_, vdim_, padded_dim()}, DType::F32).as<float>();
+            decay = ws.get("la_chunk_decay", {n_chunks, heads_, dim_}, DType::F32).as<float>();
+        }
+        if (LaunchProfile::get().on())      // q, k and v in, o out, the state in and out
+            LaunchProfile::get().note_cost((double)T * ((2 * key_width_ + value_width_) * es + value_width_ * 4.0) + 2.0 * ctx.S * per_slot * 4.0,
+                                           (double)T * heads_ * dim_ * vdim_ * 5.0);
+        QE_LAUNCH(k, k.decayed_scan(base, base + key_width_ * es, base + 2 * key_width_ * es, nullptr, qkvg.code(), width, nullptr, 0, nullptr,
+                                    1.0f, 1.0f, nullptr, (float)eps_, cache.state.as<float>(), per_slot, ctx.seg_start, ctx.seg_slot, ctx.S, T,
+                                    heads_, dim_, vdim_, n_chunks ? chunks.data : nullptr, n_chunks, n_chunks ? seg_chunks.data : nullptr,
+                                    carry, decay, raw.as<float>(), nullptr, decay_.as<float>(), 1, 1, ctx.stream));
+        if (LaunchProfile::get().on()) LaunchProfile::get().note_cost((double)T * value_width_ * (4.0 + 2.0 * es), 0.0);
+        QE_LAUNCH(k, k.rms_gate(raw.as<float>(), norm_.as<float>(), (float)eps_, base + (2 * key_width_ + value_width_) * es, qkvg.code(), width,
+                                1, y.data, y.code(), T, (int)value_width_, ctx.stream));
+        return o_proj_(y, ctx, "la_out", DType::F32, T, true, false, ctx.residual, nullptr, &ctx.norm_ahead);
+    }
+
+private:
+    static constexpr int kChunk = 64;           // tokens of a chunk of the recurrence
+    static constexpr int kChunkFrom = 128;      // the longest portion of a step from which the recurrence runs in chunks
+    int64_t hidden_, key_width_, value_width_;
+    int heads_, dim_, vdim_;
+    double eps_;
+    std::string gemm_;
+    std::vector<float> decay_host_;
+    Linear qkvg_proj_, o_proj_;
+    Tensor decay_, norm_;
 };
 
 // params: hidden_size, eps, factor (default 0.5), left {kind, params}, right {kind, params}, names{left_norm, right_norm}.
@@ -229,6 +348,7 @@ private:
 };
 
 void register_linear_attention_parts() {
+    register_part("mixer", "lightning_attention", [](const Json& p, BuildContext& b) { return std::make_shared<LightningAttention>(p, b); });
     register_part("mixer", "gated_linear_attention", [](const Json& p, BuildContext& b) { return std::make_shared<GatedLinearAttention>(p, b); });
     register_part("mixer", "side_by_side", [](const Json& p, BuildContext& b) { return std::make_shared<SideBySide>(p, b); });
 }

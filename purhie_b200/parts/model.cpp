@@ -91,13 +91,22 @@ Tensor DecoderModel::forward(StepContext& ctx, const std::vector<CacheView>& vie
                              const std::function<void(int, ResidualStream&, StepContext&)>& after_entry) {
     ResidualStream stream;
     stream.x = embedding_->forward(ctx);
+    ctx.embedding_output = nullptr;
+    if (spec_.keep_embedding_output) {
+        // the stream is rewritten in place from here on: what the embedding gave is kept beside it
+        Tensor kept = ctx.workspace->get("embedding_output", {ctx.T, spec_.hidden_size}, DType::F32);
+        QE_CUDA(cudaMemcpyAsync(kept.data, stream.x.data, stream.x.bytes(), cudaMemcpyDeviceToDevice, ctx.stream));
+        ctx.embedding_output = kept.as<float>();
+    }
     for (size_t i = 0; i < spec_.schedule.size(); i++) {
+        ctx.pass = spec_.schedule[i].pass;
         // a layer learns which norm the next entry of the run order starts with: its last product may work ahead for it
         ctx.next_layer_norm = i + 1 < spec_.schedule.size() ? layers_[spec_.schedule[i + 1].layer]->first_norm(ctx) : NormAhead();
         layers_[spec_.schedule[i].layer]->forward(stream, ctx, views[i]);
         if (after_entry) after_entry((int)i, stream, ctx);
     }
     ctx.next_layer_norm = NormAhead();
+    ctx.pass = 0;
     if (n_want == 0) return Tensor();
     Tensor xn = final_norm_->forward(stream, ctx, want_rows, n_want);
     return head_->forward(xn, ctx, n_want);

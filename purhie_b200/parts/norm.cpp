@@ -10,6 +10,21 @@ namespace qe {
 AddendTransform Norm::as_transform(float) const {
     throw ConfigError("this norm cannot be applied to an addend on its way into the residual");
 }
+void Norm::apply_in_place(Tensor&, StepContext&, int) {
+    throw ConfigError("this norm cannot be applied to rows in place");
+}
+
+void fold_second_addend(ResidualStream& stream, StepContext& ctx) {
+    if (!stream.has_also) return;
+    const Addend& b = stream.also;
+    const int64_t E = stream.x.shape[1];
+    const CoreKernels& k = core_kernels();
+    if (LaunchProfile::get().on()) LaunchProfile::get().note_cost((double)ctx.T * E * (8.0 + b.splits * dtype_size(b.tensor.dtype)), 0.0);
+    QE_LAUNCH(k, k.add_dyntanh(stream.x.as<float>(), b.tensor.data, b.tensor.code(), b.splits, (long long)ctx.T * E, nullptr, 0, 1, 0, nullptr,
+                               nullptr, nullptr, nullptr, ctx.T, (int)E, nullptr, 0, 1, ctx.stream));
+    stream.has_also = false;
+    stream.also = Addend();
+}
 
 namespace {
 // what a norm's pass over the rows moves: the residual read (and written back when an addend is folded in), the
@@ -23,6 +38,7 @@ void note_norm_cost(const ResidualStream& stream, int rows, int64_t width, DType
 // x += factor * norm(addend) for a pending addend with a transform, by the kernel that knows transforms; afterwards
 // the stream has nothing pending.  For norms whose own kernel does not know them.
 void fold_transformed(ResidualStream& stream, StepContext& ctx) {
+    fold_second_addend(stream, ctx);
     if (!stream.has_pending || !stream.pending.transform.defined()) return;
     const Addend& a = stream.pending;
     const int64_t E = stream.x.shape[1];
@@ -33,6 +49,17 @@ void fold_transformed(ResidualStream& stream, StepContext& ctx) {
     stream.clear();
 }
 }  // namespace
+
+void fold_all_addends(ResidualStream& stream, StepContext& ctx) {
+    fold_transformed(stream, ctx);            // the second addend, and a pending one that carries a transform
+    if (!stream.has_pending) return;
+    const Addend& a = stream.pending;
+    const int64_t E = stream.x.shape[1];
+    const CoreKernels& k = core_kernels();
+    QE_LAUNCH(k, k.add_dyntanh(stream.x.as<float>(), a.tensor.data, a.tensor.code(), a.splits, (long long)ctx.T * E, nullptr, 0, 1, 0, nullptr,
+                               nullptr, nullptr, nullptr, ctx.T, (int)E, nullptr, 0, 1, ctx.stream));
+    stream.clear();
+}
 
 // params: size, eps, names{weight}.
 class RMSNorm : public Norm {
@@ -61,7 +88,7 @@ public:
     // into the factor (bfloat16 model, rows of a multiple of four elements; else the ordinary form).
     Tensor forward_unscaled(ResidualStream& stream, StepContext& ctx, RowScale* scale) override {
         *scale = RowScale();
-        if (stream.prepared.done() && stream.prepared.norm == this && !stream.has_pending) {
+        if (stream.prepared.done() && stream.prepared.norm == this && !stream.has_pending && !stream.has_also) {
             // the product that added into the stream did this norm's pass in its epilogue
             Tensor rows = stream.prepared.rows;
             *scale = stream.prepared.scale;
@@ -120,6 +147,7 @@ public:
     }
     Tensor forward(ResidualStream& stream, StepContext& ctx, const int32_t* rows, int n_rows) override {
         const int n = rows ? n_rows : ctx.T;
+        fold_second_addend(stream, ctx);
         Tensor out = ctx.workspace->get(rows ? "normed_rows" : "normed", {n, size_}, compute_dtype);
         const CoreKernels& k = core_kernels();
         const Addend* a = stream.has_pending ? &stream.pending : nullptr;
@@ -154,6 +182,7 @@ public:
     }
     Tensor forward(ResidualStream& stream, StepContext& ctx, const int32_t* rows, int n_rows) override {
         const int n = rows ? n_rows : ctx.T;
+        fold_second_addend(stream, ctx);
         Tensor out = ctx.workspace->get(rows ? "normed_rows" : "normed", {n, size_}, compute_dtype);
         const CoreKernels& k = core_kernels();
         const Addend* a = stream.has_pending ? &stream.pending : nullptr;
@@ -169,7 +198,57 @@ private:
     int64_t size_;
 };
 
+// Dynamic tanh in the place of a norm: y = tanh(alpha * v) * w + b with a scalar alpha, v = x + what waits to be added.
+// It takes no statistic of the row (and has no eps).  Both addends of a layer whose two parts read the same rows are
+// folded in the same pass.  params: size, names{weight, bias, alpha}.
+class DynamicTanh : public Norm {
+public:
+    DynamicTanh(const Json& p, BuildContext& b) : Norm(p, b), size_(p.at("size").as_int()) {
+        if (size_ < 1) throw ConfigError("dyntanh: size must be positive");
+    }
+    std::vector<TensorSpec> tensor_specs() const override {
+        return {{name_of("weight"), {size_}, Role::Vector, Init::Scale}, {name_of("bias"), {size_}, Role::Vector, Init::Normal},
+                {name_of("alpha"), {}, Role::Vector, Init::Scale}};
+    }
+    void bind(WeightSource& src) override {
+        weight_ = src.fetch(name_of("weight"));
+        bias_ = src.fetch(name_of("bias"));
+        alpha_ = src.fetch(name_of("alpha"));
+    }
+    Tensor forward(ResidualStream& stream, StepContext& ctx, const int32_t* rows, int n_rows) override {
+        const int n = rows ? n_rows : ctx.T;
+        if (stream.has_pending && stream.pending.transform.defined()) fold_all_addends(stream, ctx);
+        Tensor out = ctx.workspace->get(rows ? "normed_rows" : "normed", {n, size_}, compute_dtype);
+        const CoreKernels& k = core_kernels();
+        const Addend* a = stream.has_pending ? &stream.pending : nullptr;
+        const Addend* b = stream.has_also ? &stream.also : nullptr;
+        if (LaunchProfile::get().on()) {
+            double bytes = 4.0 * n * size_ + (double)n * size_ * dtype_size(compute_dtype);
+            if (a) bytes += (double)a->splits * n * size_ * dtype_size(a->tensor.dtype);
+            if (b) bytes += (double)b->splits * n * size_ * dtype_size(b->tensor.dtype);
+            if ((a || b) && !rows) bytes += 4.0 * n * size_;
+            LaunchProfile::get().note_cost(bytes, 0.0);
+        }
+        QE_LAUNCH(k, k.add_dyntanh(stream.x.as<float>(), a ? a->tensor.data : nullptr, a ? a->tensor.code() : 0, a ? a->splits : 1,
+                                   a ? (long long)ctx.T * size_ : 0, b ? b->tensor.data : nullptr, b ? b->tensor.code() : 0,
+                                   b ? b->splits : 1, b ? (long long)ctx.T * size_ : 0, alpha_.as<float>(), weight_.as<float>(),
+                                   bias_.as<float>(), rows, n, (int)size_, out.data, out.code(), (!rows && (a || b)) ? 1 : 0, ctx.stream));
+        if (!rows) stream.clear();
+        return out;
+    }
+    void apply_in_place(Tensor& x, StepContext& ctx, int n) override {
+        const CoreKernels& k = core_kernels();
+        if (LaunchProfile::get().on()) LaunchProfile::get().note_cost(8.0 * n * size_, 0.0);
+        QE_LAUNCH(k, k.add_dyntanh(x.as<float>(), nullptr, 0, 1, 0, nullptr, 0, 1, 0, alpha_.as<float>(), weight_.as<float>(), bias_.as<float>(),
+                                   nullptr, n, (int)size_, x.data, x.code(), 0, ctx.stream));
+    }
+private:
+    int64_t size_;
+    Tensor weight_, bias_, alpha_;
+};
+
 void register_norm_parts() {
+    register_part("norm", "dyntanh", [](const Json& p, BuildContext& b) { return std::make_shared<DynamicTanh>(p, b); });
     register_part("norm", "rmsnorm", [](const Json& p, BuildContext& b) { return std::make_shared<RMSNorm>(p, b); });
     register_part("norm", "layernorm", [](const Json& p, BuildContext& b) { return std::make_shared<LayerNorm>(p, b); });
     register_part("norm", "none", [](const Json& p, BuildContext& b) { return std::make_shared<NoNorm>(p, b); });

@@ -74,7 +74,8 @@ struct CacheNeed {
     int value_dim = 0;                            // pages: width of a value row when it differs from a key row's (0: head_dim)
     int window = 0;                               // pages: 0 keeps all keys, W keeps the last W positions
     int chunk = 0;                                // pages: C > 0 keeps the keys of the block of C positions (counted from 0) that the next position is in
-    int v_dim() const { return value_dim > 0 ? value_dim : head_dim; }
+    bool keys_only = false;                       // pages: no value rows are kept (the mixer reads its values out of the key rows)
+    int v_dim() const { return keys_only ? 0 : value_dim > 0 ? value_dim : head_dim; }
     std::vector<int64_t> state_shape;             // state: shape of one request's state (a mixer of pages may keep one too)
     DType state_dtype = DType::F32;
     bool has_state() const { return !state_shape.empty(); }
@@ -84,6 +85,12 @@ struct CacheNeed {
         if (kv_heads < 1 || head_dim < 1 || value_dim < 0) throw Error(kInvalidArg, "a page holds at least one head of at least one element");
         CacheNeed n; n.kind = Pages; n.kv_heads = kv_heads; n.head_dim = head_dim; n.window = window; n.chunk = chunk;
         n.value_dim = value_dim == head_dim ? 0 : value_dim;
+        return n;
+    }
+    // Pages of one row per token and nothing else: a mixer whose keys and values are both made from that row.
+    static CacheNeed rows(int width, int window = 0) {
+        CacheNeed n = pages(1, width, window);
+        n.keys_only = true;
         return n;
     }
     static CacheNeed state(std::vector<int64_t> shape, DType dtype = DType::F32) {
@@ -127,12 +134,14 @@ struct LayerSpec {
 struct LayerCall {
     int layer = 0;               // index into ModelSpec::layers
     int cache_from = -1;         // -1: a cache entry of its own; else the earlier call whose cache this one reads
+    int pass = 0;                // which time round a repeated stretch of layers this call belongs to (StepContext::pass)
 };
 
 struct ModelSpec {
     int64_t hidden_size = 0, vocab_size = 0, max_position = 0;
     int position_columns = 1;    // columns of positions a step carries per row (column 0: the index in the request)
     PartSpec embedding, final_norm, head;
+    bool keep_embedding_output = false;   // the rows the embedding gave stay readable for the whole step (StepContext::embedding_output)
     std::vector<LayerSpec> layers;
     std::vector<LayerCall> schedule;
     void validate() const;
@@ -240,6 +249,8 @@ struct StepContext {
     RowScale row_scale;                      // set by an arrangement around a consumer that takes unscaled rows, else undefined
     NormAhead norm_ahead;                    // set by an arrangement around a part: the norm after the part's addition
     NormAhead next_layer_norm;               // set by the model around a layer: the first norm of the layer that runs next
+    int pass = 0;                            // LayerCall::pass of the run-order entry that is running
+    const float* embedding_output = nullptr; // [T, E] float32, what the embedding gave (only where the model keeps it)
     std::map<std::string, StepArray> arrays; // what parts added through StepPlan, by name
     const Json* options = nullptr;           // kernel choices for tests ("decode_kernel": "cp_async", ...)
 
@@ -271,15 +282,24 @@ struct ResidualStream {
     Tensor x;
     Addend pending;
     bool has_pending = false;
+    Addend also;                             // a second addend (a layer whose two parts read the same rows), without a transform
+    bool has_also = false;
     NormAhead prepared;                      // rows that the last product left for the norm that comes next (x is complete)
     void add(Addend a) {
         if (has_pending) throw Error(kInvalidState, "the residual stream already has a pending addend");
         prepared = NormAhead();
         if (a.tensor.defined()) { pending = std::move(a); has_pending = true; }   // undefined: the part added into x itself
     }
+    // a second addend beside the pending one; whoever folds the pending addend in folds this one too
+    void add_also(Addend a) {
+        if (has_also) throw Error(kInvalidState, "the residual stream already has a second addend");
+        if (a.transform.defined()) throw Error(kInvalidState, "a second addend carries no transform");
+        prepared = NormAhead();
+        if (a.tensor.defined()) { also = std::move(a); has_also = true; }
+    }
     // after add(): what the part's last product did for the norm ahead (nothing, if it did nothing)
-    void prepare(const NormAhead& ahead) { prepared = (!has_pending && ahead.done()) ? ahead : NormAhead(); }
-    void clear() { has_pending = false; pending = Addend(); prepared = NormAhead(); }
+    void prepare(const NormAhead& ahead) { prepared = (!has_pending && !has_also && ahead.done()) ? ahead : NormAhead(); }
+    void clear() { has_pending = false; pending = Addend(); has_also = false; also = Addend(); prepared = NormAhead(); }
 };
 
 // ---- building ---------------------------------------------------------------------------------------------------
@@ -335,7 +355,15 @@ public:
     // This norm as a transform of an addend (AddendTransform) with the given factor, for a layer that norms what a
     // part gives before adding it; a norm that has no such form throws.
     virtual AddendTransform as_transform(float factor) const;
+    // The float32 rows x [n, width] normed in place (no addend, no cast): for an embedding that is normed before it
+    // becomes the residual stream.  A norm that has no such form throws.
+    virtual void apply_in_place(Tensor& x, StepContext& ctx, int n);
 };
+
+// x += the stream's second addend, for a norm whose own kernel folds one addend only (no-op without one).
+QE_API void fold_second_addend(ResidualStream& stream, StepContext& ctx);
+// x += every addend that waits (transform included): afterwards the stream's x is complete and nothing is pending.
+QE_API void fold_all_addends(ResidualStream& stream, StepContext& ctx);
 
 class QE_API PositionEncoding : public Part {
 public:
@@ -408,8 +436,9 @@ template <typename T> std::shared_ptr<T> make_part_as(const std::string& family,
     return p;
 }
 
-// Registers the parts this library brings (rmsnorm, layernorm, rope_neox, attention, mamba1, swiglu, routed_glu,
-// embedding, lm_head, pre_norm, sandwich_norm).
+// Registers the parts this library brings (rmsnorm, layernorm, none, dyntanh, rope_neox, attention, latent_attention,
+// mamba1, gated_linear_attention, lightning_attention, side_by_side, swiglu, mlp, routed_glu, embedding, lm_head,
+// pre_norm, sandwich_norm, parallel, reinject).
 QE_API void register_builtin_parts();
 
 }  // namespace qe

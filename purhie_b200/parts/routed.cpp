@@ -8,7 +8,10 @@
 // Other designs' options: "scoring": {"kind": "sigmoid", "groups", "keep"}: scores s = sigmoid(z); the choice goes by
 // s + correction (a vector per expert, names.correction; without it by s), restricted to the `keep` runs of neighbouring
 // experts (of `groups` equal runs) whose two largest choice values add up highest; the weights are the chosen
-// experts' s as they are.  "gated": false: an expert is Wd act(Wu x) with an activation of one argument ("relu2").
+// experts' s as they are.  {"kind": "softmax", "groups", "keep", "scale"}: s = softmax(z) over all experts; the choice goes by
+// s within the `keep` runs whose largest s is highest; the weights are the chosen s over their sum (+ 1e-20), times `scale`.
+// names.shared_gate (a vector [hidden]): the shared part's sum is multiplied by sigmoid(gate . x), one number per token.
+// "gated": false: an expert is Wd act(Wu x) with an activation of one argument ("relu2").
 // "shared": {kind, params}: a feed-forward that runs for every token and is added to the chosen experts' sum.
 //
 // The (token, choice) pairs are sorted by expert on the device.  Which kernels then multiply:
@@ -31,7 +34,7 @@ namespace qe {
 
 // params: hidden_size, intermediate_size, experts, top, gated (default true), activation (as the gated feed-forward's;
 // without a gate a name as the plain feed-forward's), scoring (null or as above), shared (null or {kind, params}),
-// names{router, router_bias (optional), correction (optional)}, expert_names [{gate_proj, up_proj, down_proj} per
+// names{router, router_bias (optional), correction (optional), shared_gate (optional)}, expert_names [{gate_proj, up_proj, down_proj} per
 // expert; without a gate {up_proj, down_proj}].
 class RoutedGLU : public FeedForward {
 public:
@@ -53,8 +56,11 @@ public:
         if (const Json* sc = p.find("scoring")) {
             if (!sc->is_null()) {
                 const std::string kind = sc->get_string("kind", "");
-                if (kind != "sigmoid") throw ConfigError("routed feed-forward: scoring of kind '" + kind + "' is not known (sigmoid is)");
-                scoring_ = 1;
+                if (kind != "sigmoid" && kind != "softmax")
+                    throw ConfigError("routed feed-forward: scoring of kind '" + kind + "' is not known (sigmoid, softmax)");
+                scoring_ = kind == "sigmoid" ? 1 : 2;
+                weight_scale_ = (float)sc->get_double("scale", 1.0);
+                if (scoring_ != 2 && weight_scale_ != 1.0f) throw ConfigError("routed feed-forward: only softmax scoring scales its weights");
                 groups_ = (int)sc->get_int("groups", 1);
                 keep_ = (int)sc->get_int("keep", groups_);
                 if (groups_ < 1 || experts_ % groups_ || keep_ < 1 || keep_ > groups_ || (long long)keep_ * (experts_ / groups_) < top_)
@@ -62,15 +68,18 @@ public:
                                       std::to_string(experts_) + " experts cannot give " + std::to_string(top_) + " choices");
             }
         }
-        if (has_correction_ && !scoring_) throw ConfigError("routed feed-forward: a correction of the choice needs sigmoid scoring");
+        has_shared_gate_ = names_.count("shared_gate") != 0;
+        if (has_correction_ && scoring_ != 1) throw ConfigError("routed feed-forward: a correction of the choice needs sigmoid scoring");
         if (const Json* sh = p.find("shared"))
             if (!sh->is_null()) shared_ = make_part_as<FeedForward>("feed_forward", PartSpec::from_json(*sh), b);
+        if (has_shared_gate_ && !shared_) throw ConfigError("routed feed-forward: a gate of the shared part needs a shared part");
     }
 
     std::vector<TensorSpec> tensor_specs() const override {
         std::vector<TensorSpec> s = {{name_of("router"), {experts_, hidden_}, Role::Vector, Init::Normal}};
         if (has_bias_) s.push_back({name_of("router_bias"), {experts_}, Role::Vector, Init::Normal});
         if (has_correction_) s.push_back({name_of("correction"), {experts_}, Role::Vector, Init::Normal});
+        if (has_shared_gate_) s.push_back({name_of("shared_gate"), {1, hidden_}, Role::Vector, Init::Normal});
         for (const auto& n : expert_names_) {
             if (gated_) s.push_back({n[0], {inter_, hidden_}, Role::Matrix, Init::Normal});
             s.push_back({n[1], {inter_, hidden_}, Role::Matrix, Init::Normal});
@@ -83,6 +92,7 @@ public:
         router_ = src.fetch(name_of("router"));
         if (has_bias_) router_bias_ = src.fetch(name_of("router_bias"));
         if (has_correction_) correction_ = src.fetch(name_of("correction"));
+        if (has_shared_gate_) shared_gate_ = src.fetch(name_of("shared_gate"));
         if (shared_) shared_->bind(src);
         // the experts' matrices stacked: [experts, 2 ff, hidden] with gate and up rows interleaved (g0, u0, g1, u1, ...)
         // as the gated feed-forward lays them out (without a gate [experts, ff, hidden]), and [experts, hidden, ff]
@@ -153,9 +163,12 @@ public:
             if (always.tensor.defined() && (always.tensor.dtype != DType::F32 || always.transform.defined()))
                 throw Error(kInvalidState, "routed feed-forward: the shared part must give float32 sums without a transform");
         }
+        // sigmoid(gate . x) per token for the shared part's sum: one more row of the router's product
+        float* shared_scale = shared_gate_.defined() ? ws.get("moe_shared_scale", {T}, DType::F32).as<float>() : nullptr;
         QE_LAUNCH(k, k.route(x.data, x.code(), router_.as<float>(), router_bias_.defined() ? router_bias_.as<float>() : nullptr, T, experts_,
                              (int)hidden_, top_, choice.as<int32_t>(), weight.as<float>(), scoring_,
-                             correction_.defined() ? correction_.as<float>() : nullptr, groups_, keep_, ctx.stream));
+                             correction_.defined() ? correction_.as<float>() : nullptr, groups_, keep_, weight_scale_,
+                             shared_gate_.defined() ? shared_gate_.as<float>() : nullptr, shared_scale, ctx.stream));
         const int tiles = k.route_max_tiles(R, experts_);
         Tensor position = ws.get("moe_position", {R}, DType::I32), pair_at = ws.get("moe_pair_at", {R}, DType::I32);
         Tensor tile_list = ws.get("moe_tiles", {tiles, 3}, DType::I32), scratch = ws.get("moe_sort_scratch", {3 * experts_ + 1}, DType::I32);
@@ -214,7 +227,7 @@ public:
         Tensor out = ws.get("moe_out", {T, hidden_}, DType::F32);
         QE_LAUNCH(k, k.route_combine(y.data, y.code(), position.as<int32_t>(), weight.as<float>(), T, top_, (int)hidden_, out.as<float>(),
                                      always.tensor.defined() ? always.tensor.as<float>() : nullptr, always.tensor.defined() ? always.splits : 0,
-                                     (long long)T * hidden_, ctx.stream));
+                                     (long long)T * hidden_, always.tensor.defined() ? shared_scale : nullptr, ctx.stream));
         return Addend(out, 1);
     }
 
@@ -224,13 +237,15 @@ private:
     int experts_, top_;
     GateSpec gate_;
     bool gated_ = true, has_bias_ = false, has_correction_ = false;
+    bool has_shared_gate_ = false;
     int unary_ = 0, scoring_ = 0, groups_ = 1, keep_ = 1;
+    float weight_scale_ = 1.0f;
     int64_t up_width_ = 0;
     std::shared_ptr<FeedForward> shared_;
     std::vector<std::array<std::string, 3>> expert_names_;
     std::vector<Linear> expert_gate_up_, expert_down_;
     PinnedBuffer counts_host_;
-    Tensor router_, router_bias_, correction_, gate_up_, down_;
+    Tensor router_, router_bias_, correction_, shared_gate_, gate_up_, down_;
 };
 
 void register_routed_parts() {
