@@ -2,7 +2,7 @@
 """Decode and prefill throughput of the engine at the Qwen3-8B shape with random weights, on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--shape 8b|0.6b|32b] [--impl ours|reference]
-    python bench.py --design bozosun|sizizen [--size 2k|4k]   (another design beside the Qwen3 layers of equal size; see below)
+    python bench.py --design bozosun|sizizen|zerusun [--size 2k|4k]   (another design beside the Qwen3 layers of equal size; see below)
 
 Prints ONE JSON line.  ``value`` is decoded tokens per second at batch 8 from 2,048-token prefixes, timed on the
 device (CUDA events on the engine's stream) over exactly K decode steps after W warm-up steps, each step fed its
@@ -132,7 +132,27 @@ def sizizen_config(z):
     return {"architecture": "Sizizen", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6}, "layers": layers, "max_position": CONTEXT}
 
 
-DESIGN_CONFIGS = {"bozosun": bozosun_config, "sizizen": sizizen_config}
+def zerusun_config(z):
+    """Four parallel layers under dynamic-tanh norms: attention through a latent (query latent of 3/4 of the width, a
+    cached row of 512 + 64 numbers, heads of 128 + 64 rotated dimensions, a window of 1,024 positions) in the first and
+    last, lightning attention with half as many heads of 128 x 128 state in between; a dense gated unit in the first and
+    last, routed experts with a gated shared one in between.  The two middle layers are the repeated stretch, run once,
+    so that the reinjection in front of it is in the step and the number of layer runs equals the twin's."""
+    rot = {"base": 5e5, "dims": 64, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+    latent = {"heads": z["heads"], "dim": z["dim"], "rot_dim": 64, "vdim": z["dim"], "q_rank": 3 * z["width"] // 4, "kv_rank": 512,
+              "mask": {"size": 1024}, "rot": rot, "scale": (z["dim"] + 64) ** -0.5}
+    heads = z["heads"] // 2
+    lightning = {"heads": heads, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** (-3.0 - 5.0 * h / max(heads - 1, 1)) for h in range(heads)]}
+    dense = {"kind": "dense", "ff": z["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "shared": {"ff": z["expert_ff"]},
+           "router": {"experts": z["experts"], "top": z["top"], "scale": 2.5, "groups": {"count": 4, "keep": 2}}}
+    layers = [{"type": "latent_attention", "mixer": latent, "mlp": dense}, {"type": "lightning", "mixer": lightning, "mlp": moe},
+              {"type": "lightning", "mixer": lightning, "mlp": moe}, {"type": "latent_attention", "mixer": latent, "mlp": dense}]
+    return {"architecture": "Zerusun", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6}, "layers": layers,
+            "loop": {"start": 1, "stop": 3, "times": 1}, "max_position": CONTEXT}
+
+
+DESIGN_CONFIGS = {"bozosun": bozosun_config, "sizizen": sizizen_config, "zerusun": zerusun_config}
 
 
 def design_bench(args):
@@ -222,7 +242,7 @@ def main():
     ap.add_argument("--page-size", type=int, default=16, help="tokens per cache page (the benchmark's configuration has 16)")
     ap.add_argument("--step-options", default="", metavar="JSON",
                     help="kernel choices of the step, for comparing two forms of it on one box, e.g. '{\"norm_ahead\": \"off\"}'")
-    ap.add_argument("--design", default="", choices=["", "bozosun", "sizizen"],
+    ap.add_argument("--design", default="", choices=["", "bozosun", "sizizen", "zerusun"],
                     help="instead of the headline workload: prefill and decode of this design at real layer sizes beside four "
                          "Qwen3 layers of equal size, with the time and roofline fraction of every kernel class")
     ap.add_argument("--size", default="4k", choices=sorted(DESIGN_SIZES), help="with --design: the layer sizes")
