@@ -41,6 +41,12 @@ LIBRARIES: Dict[str, dict] = {
         "flags": [],
         "link": [],
     },
+    "latent": {
+        "sources": ["latent_attention_mma.cu"],
+        "deps": ["attention_mma.cuh"],
+        "flags": [],
+        "link": [],
+    },
     "gemm100": {
         "sources": ["gemm_tcgen05.cu"],
         "flags": [],

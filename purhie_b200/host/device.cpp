@@ -89,7 +89,8 @@ std::map<std::string, void*> g_handles;
 CoreKernels g_core{};
 FlashKernels g_flash{};
 GemmKernels g_gemm{};
-bool g_core_ok = false, g_flash_ok = false, g_gemm_ok = false;
+LatentKernels g_latent{};
+bool g_core_ok = false, g_flash_ok = false, g_gemm_ok = false, g_latent_ok = false;
 
 std::string own_dir() {
     Dl_info info;
@@ -208,10 +209,25 @@ const GemmKernels& gemm_kernels() {
     return g_gemm;
 }
 
+const LatentKernels& latent_kernels() {
+    if (g_latent_ok) return g_latent;
+    std::lock_guard<std::mutex> lock(g_lib_mutex);
+    if (g_latent_ok) return g_latent;
+    void* h = open_library("latent");
+    bind(h, "latent", "ph_latent_attention_supports", g_latent.supports);
+    bind(h, "latent", "ph_latent_attention", g_latent.attention);
+    bind(h, "latent", "ph_latent_absorb_mma", g_latent.latent_absorb);
+    bind(h, "latent", "ph_latent_expand_mma", g_latent.latent_expand);
+    bind(h, "latent", "ph_latent_last_error", g_latent.last_error);
+    g_latent_ok = true;
+    return g_latent;
+}
+
 void require_library(const std::string& name) {
     if (name == "core") core_kernels();
     else if (name == "flash") flash_kernels();
     else if (name == "gemm100") gemm_kernels();
+    else if (name == "latent") latent_kernels();
     else {
         std::lock_guard<std::mutex> lock(g_lib_mutex);
         open_library(name);

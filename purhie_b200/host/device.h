@@ -169,6 +169,16 @@ struct FlashKernels {
                        float*, int*, cudaStream_t);
     const char* (*last_error)(void);
 };
+// attention over cached latent rows on the tensor cores (latent_attention_mma.cu)
+struct LatentKernels {
+    int (*supports)(int, int);
+    int (*attention)(const void*, const void*, long long, int, const int32_t*, int, const int32_t*, const int32_t*, const int32_t*,
+                     const int32_t*, int, void*, float*, float*, int, int, int, int, float, int, cudaStream_t);
+    // the products per head in front of and behind it
+    int (*latent_absorb)(const void*, const void*, const float*, int, int, const int32_t*, void*, int, int, int, int, int, cudaStream_t);
+    int (*latent_expand)(const void*, const void*, const void*, long long, void*, int, int, int, int, cudaStream_t);
+    const char* (*last_error)(void);
+};
 struct GemmKernels {
     int (*gemm)(const void*, const void*, void*, int, int, int, int, int, int, int, int, int, const float*, int, const float*, int, int,
                 float, const float*, void*, float*, int*, cudaStream_t);
@@ -184,7 +194,8 @@ QE_API std::string library_dir();
 QE_API const CoreKernels& core_kernels();
 QE_API const FlashKernels& flash_kernels();
 QE_API const GemmKernels& gemm_kernels();
-QE_API void require_library(const std::string& name);      // "core", "flash", "gemm100": open it now
+QE_API const LatentKernels& latent_kernels();
+QE_API void require_library(const std::string& name);      // "core", "flash", "gemm100", "latent": open it now
 QE_API extern long long g_launches;                          // launcher calls so far (for the bench's count)
 
 // Time per kernel class, for finding out where a step's time goes (the reference prints such a breakdown under

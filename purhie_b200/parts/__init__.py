@@ -82,6 +82,7 @@ class PartProbe:
         if dtype == "bfloat16":
             native.build_library("flash")
             native.build_library("gemm100")
+            native.build_library("latent")
         spec = json.dumps({"kind": kind, "params": params}).encode()
         self._h = _lib().qe_part_create(family.encode(), spec, dtype.encode(), json.dumps(options or {}).encode())
         if not self._h:
