@@ -121,11 +121,12 @@ __global__ void __launch_bounds__(LA_THREADS, 1) latent_attention_kernel(
         const int key0 = kb * BK;
         const bool rows_here = rg * 16 < n_rows;                     // a row group beyond the tile's rows only helps to load
         if (rows_here) {   // scores of this warp's half of the keys
-            float s[NKW / 8][4];
+            // even and odd steps of the contraction add into sums of their own: twice as many independent chains of mma
+            float s[NKW / 8][4], s2[NKW / 8][4];
 #pragma unroll
             for (int nt = 0; nt < NKW / 8; ++nt)
 #pragma unroll
-                for (int i = 0; i < 4; ++i) s[nt][i] = 0.0f;
+                for (int i = 0; i < 4; ++i) s[nt][i] = s2[nt][i] = 0.0f;
 #pragma unroll 4
             for (int ks = 0; ks < L::DK / 16; ++ks) {
                 uint32_t a0, a1, a2, a3;
@@ -135,10 +136,19 @@ __global__ void __launch_bounds__(LA_THREADS, 1) latent_attention_kernel(
                     uint32_t b0, b1, b2, b3;
                     const int row = half * NKW + nt * 8 + (lane & 7) + ((lane >> 4) << 3);
                     ldmatrix_x4(k_tile + row * PITCH + (ks * 2 + ((lane >> 3) & 1)) * 16, b0, b1, b2, b3);
-                    mma_bf16(s[nt], a0, a1, a2, a3, b0, b1);
-                    mma_bf16(s[nt + 1], a0, a1, a2, a3, b2, b3);
+                    if (ks & 1) {
+                        mma_bf16(s2[nt], a0, a1, a2, a3, b0, b1);
+                        mma_bf16(s2[nt + 1], a0, a1, a2, a3, b2, b3);
+                    } else {
+                        mma_bf16(s[nt], a0, a1, a2, a3, b0, b1);
+                        mma_bf16(s[nt + 1], a0, a1, a2, a3, b2, b3);
+                    }
                 }
             }
+#pragma unroll
+            for (int nt = 0; nt < NKW / 8; ++nt)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) s[nt][i] += s2[nt][i];
 #pragma unroll
             for (int nt = 0; nt < NKW / 8; ++nt) {
                 const int col = half * NKW + nt * 8 + (lane & 3) * 2;
