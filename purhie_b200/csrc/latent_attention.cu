@@ -25,7 +25,7 @@ using namespace ph;
 __device__ __forceinline__ float turn_u(float u, float v, float c, float s) { return u * c - v * s; }
 __device__ __forceinline__ float turn_v(float u, float v, float c, float s) { return v * c + u * s; }
 
-constexpr int PREP_WARPS = 4;
+constexpr int PREP_THREADS = 128;      // a block per token: its threads walk the latents 128 apart
 
 template <typename TD, typename TQ, typename TKV>
 __global__ void latent_prepare_kernel(const TD* __restrict__ down, long long down_stride, int Q, int C, int R,
@@ -33,31 +33,31 @@ __global__ void latent_prepare_kernel(const TD* __restrict__ down, long long dow
                                       const float* __restrict__ cos_sin, int n_rot, int max_pos, const int32_t* __restrict__ positions,
                                       const int32_t* __restrict__ slot_mapping, TQ* __restrict__ cq, TKV* __restrict__ k_base,
                                       long long page_stride, int page_size, int T) {
+    __shared__ float scratch[32];
     pdl_launch_dependents();
     pdl_wait();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x * PREP_WARPS + warp;
-    if (t >= T) return;
+    const int lane = threadIdx.x;
+    const int t = blockIdx.x;
     const TD* row = down + (size_t)t * down_stride;
     // the query latent
     float ss = 0.0f;
-    for (int i = lane; i < Q; i += 32) { const float v = to_float<TD>(row[i]); ss += v * v; }
-    float inv = rsqrtf(warp_sum(ss) / (float)Q + eps);
-    for (int i = lane; i < Q; i += 32) cq[(size_t)t * Q + i] = from_float<TQ>(to_float<TD>(row[i]) * inv * wq[i]);
+    for (int i = lane; i < Q; i += PREP_THREADS) { const float v = to_float<TD>(row[i]); ss += v * v; }
+    float inv = rsqrtf(block_sum<PREP_THREADS>(ss, scratch) / (float)Q + eps);
+    for (int i = lane; i < Q; i += PREP_THREADS) cq[(size_t)t * Q + i] = from_float<TQ>(to_float<TD>(row[i]) * inv * wq[i]);
     if (!slot_mapping) return;
     // the kv latent and the shared rotated key part, into the token's cache row
     const int slot = slot_mapping[t];
     TKV* dst = k_base + (size_t)(slot / page_size) * page_stride + (size_t)(slot % page_size) * (C + R);
     ss = 0.0f;
-    for (int i = lane; i < C; i += 32) { const float v = to_float<TD>(row[Q + i]); ss += v * v; }
-    inv = rsqrtf(warp_sum(ss) / (float)C + eps);
-    for (int i = lane; i < C; i += 32) dst[i] = from_float<TKV>(to_float<TD>(row[Q + i]) * inv * wkv[i]);
+    for (int i = lane; i < C; i += PREP_THREADS) { const float v = to_float<TD>(row[Q + i]); ss += v * v; }
+    inv = rsqrtf(block_sum<PREP_THREADS>(ss, scratch) / (float)C + eps);
+    for (int i = lane; i < C; i += PREP_THREADS) dst[i] = from_float<TKV>(to_float<TD>(row[Q + i]) * inv * wkv[i]);
     int pos = positions[t];
     pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);     // positions are validated on the host
     const float* cs = cos_sin + (size_t)pos * n_rot;
     const int half = n_rot / 2;
     const TD* r = row + Q + C;
-    for (int i = lane; i < R; i += 32) {
+    for (int i = lane; i < R; i += PREP_THREADS) {
         float v = to_float<TD>(r[i]);
         if (i < half) v = turn_u(v, to_float<TD>(r[i + half]), cs[i], cs[half + i]);
         else if (i < n_rot) v = turn_v(to_float<TD>(r[i - half]), v, cs[i - half], cs[i]);
@@ -164,9 +164,9 @@ PH_EXPORT int ph_latent_prepare(const void* down, int down_dtype, long long down
         (slot_mapping && (!k_base || !wkv || page_size < 1)) || !valid_dtype(down_dtype) || !valid_dtype(cq_dtype) || !valid_dtype(kv_dtype))
         return fail(PH_ERR_ARG, "latent_prepare: bad arguments (T %d, latents %d and %d, rotated %d of %d)", T, Q, C, n_rot, R);
     if (T == 0) return PH_OK;
-    const unsigned blocks = (unsigned)((T + PREP_WARPS - 1) / PREP_WARPS);
+    const unsigned blocks = (unsigned)T;
 #define LAUNCH(TD, TQ, TKV)                                                                                                       \
-    launch_overlapped(latent_prepare_kernel<TD, TQ, TKV>, dim3(blocks), dim3(PREP_WARPS * 32), 0, stream, (const TD*)down, down_stride, Q, \
+    launch_overlapped(latent_prepare_kernel<TD, TQ, TKV>, dim3(blocks), dim3(PREP_THREADS), 0, stream, (const TD*)down, down_stride, Q, \
                       C, R, wq, wkv, eps, cos_sin, n_rot, max_pos, positions, slot_mapping, (TQ*)cq, (TKV*)k_base, page_stride, page_size, T)
     PH_DISPATCH(down_dtype, TD, PH_DISPATCH(cq_dtype, TQ, PH_DISPATCH(kv_dtype, TKV, LAUNCH(TD, TQ, TKV))));
 #undef LAUNCH
