@@ -6,8 +6,8 @@
 //
 //   * latent_attention: one CTA of 8 warps per (64 query rows of one request, split of the keys).  Warp w owns
 //     the 16 rows (w & 3) * 16 .. + 15.  For every block of BK keys the two warps of a row group score half of
-//     the keys each (Q K^T over C + R, Q read from shared memory), leave the raw scores in shared memory, read
-//     back all BK, and run the same online softmax; then each adds P V for its half of the C output columns, which
+//     the keys each (Q K^T over C + R, Q read from shared memory), leave the raw scores in shared memory (a barrier of
+//     the pair), read back all BK, and run the same online softmax; then each adds P V for its half of the C output columns, which
 //     keeps the float32 accumulators at C / 2 columns per warp.
 //   * latent_attention_combine merges the splits of a tile in a fixed order.
 // Rows are held in shared memory padded to CP and RP columns (zeros), row pitch (CP + RP) * 2 + 16 bytes so that the
@@ -156,8 +156,9 @@ __global__ void __launch_bounds__(LA_THREADS, 1) latent_attention_kernel(
                 *(float2*)(s_buf + r1 * L::S_PITCH + col) = make_float2(s[nt][2], s[nt][3]);
             }
         }
-        __syncthreads();
         if (!rows_here) continue;
+        // only the two warps of a row group exchange scores: a barrier of their 64 threads (ids 1 .. 4; 0 is the CTA's)
+        asm volatile("bar.sync %0, 64;" ::"r"(1 + rg) : "memory");
         float p[BK / 8][4];
 #pragma unroll
         for (int nt = 0; nt < BK / 8; ++nt) {
