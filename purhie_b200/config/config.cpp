@@ -335,6 +335,7 @@ ModelSpec Qwen3Config::build_spec() const {
 void register_bozosun_architecture();
 void register_sizizen_architecture();
 void register_zerusun_architecture();
+void register_vokepel_architecture();
 
 void register_builtin_architectures() {
     static std::once_flag once;
@@ -343,6 +344,7 @@ void register_builtin_architectures() {
         register_bozosun_architecture();
         register_sizizen_architecture();
         register_zerusun_architecture();
+        register_vokepel_architecture();
     });
 }
 

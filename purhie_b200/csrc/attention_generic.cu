@@ -12,6 +12,8 @@
 // keeps a running maximum and sum (online softmax) and each lane owns the output dimensions d = lane,
 // lane + 32, ...  The order of every addition depends on (z, window) only, never on how the request was
 // cut into steps or on what else is in the batch.
+// A sink (one float32 number per query head, or none) is one more term exp(sink) in the softmax's denominator: it has no
+// key and no value, is not scaled, and counts once whatever the window holds.
 // Formulas (reference): src/qwen_ops.cpp:26-51 (scores * scale, max-subtracted softmax, weighted sum of
 // V; query head h uses kv head h / (HQ / HKV)); window: src/attention.h:73.
 #include "common.cuh"
@@ -30,7 +32,8 @@ __global__ void attention_generic_kernel(const TQ* __restrict__ q, const TKV* __
                                          const TKV* __restrict__ v_base, long long page_stride, int page_size,
                                          const int32_t* __restrict__ block_table, int table_stride,
                                          const int32_t* __restrict__ row_seg, const int32_t* __restrict__ positions,
-                                         TO* __restrict__ out, int T, int HQ, int HKV, int D, int window, float scale, int DV, int chunk, int VS) {
+                                         TO* __restrict__ out, int T, int HQ, int HKV, int D, int window, float scale, int DV, int chunk, int VS,
+                                         const float* __restrict__ sink) {
     __shared__ float qs[WARPS][MAX_D];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long item = (long long)blockIdx.x * WARPS + warp;
@@ -83,6 +86,13 @@ __global__ void attention_generic_kernel(const TQ* __restrict__ q, const TKV* __
         m = m_new;
     }
     TO* o = out + ((size_t)t * HQ + h) * DV;
+    if (sink) {
+        // the sink joins the denominator under the larger of the two maxima
+        const float sk = sink[h], top = fmaxf(m, sk), corr = expf(m - top);
+        l = l * corr + expf(sk - top);
+#pragma unroll
+        for (int i = 0; i < MAX_D / 32; ++i) acc[i] *= corr;
+    }
     const float inv = 1.0f / l;
 #pragma unroll
     for (int i = 0; i < MAX_D / 32; ++i) {
@@ -93,11 +103,11 @@ __global__ void attention_generic_kernel(const TQ* __restrict__ q, const TKV* __
 
 }  // namespace
 
-PH_EXPORT int ph_attention_generic(const void* q, int q_dtype, const void* k_base, const void* v_base, int kv_dtype,
-                                   long long page_stride, int page_size, const int32_t* block_table,
-                                   int table_stride, const int32_t* row_seg, const int32_t* positions, void* out,
-                                   int out_dtype, int T, int HQ, int HKV, int D, int window, float scale, int DV,
-                                   int chunk, int v_stride, cudaStream_t stream) {
+PH_EXPORT int ph_attention_generic_sink(const void* q, int q_dtype, const void* k_base, const void* v_base, int kv_dtype,
+                                        long long page_stride, int page_size, const int32_t* block_table,
+                                        int table_stride, const int32_t* row_seg, const int32_t* positions, void* out,
+                                        int out_dtype, int T, int HQ, int HKV, int D, int window, float scale, int DV,
+                                        int chunk, int v_stride, const float* sink, cudaStream_t stream) {
     if (!q || !k_base || !v_base || !block_table || !row_seg || !positions || !out || T < 0 || HQ < 1 || HKV < 1 ||
         D < 1 || page_size < 1 || window < 0 || chunk < 0 || !valid_dtype(q_dtype) || !valid_dtype(kv_dtype) ||
         !valid_dtype(out_dtype))
@@ -112,8 +122,17 @@ PH_EXPORT int ph_attention_generic(const void* q, int q_dtype, const void* k_bas
 #define LAUNCH(TQ, TKV, TO)                                                                                    \
     attention_generic_kernel<TQ, TKV, TO><<<blocks, WARPS * 32, 0, stream>>>(                                  \
         (const TQ*)q, (const TKV*)k_base, (const TKV*)v_base, page_stride, page_size, block_table, table_stride, \
-        row_seg, positions, (TO*)out, T, HQ, HKV, D, window, scale, DV, chunk, v_stride)
+        row_seg, positions, (TO*)out, T, HQ, HKV, D, window, scale, DV, chunk, v_stride, sink)
     PH_DISPATCH(q_dtype, TQ, PH_DISPATCH(kv_dtype, TKV, PH_DISPATCH(out_dtype, TO, LAUNCH(TQ, TKV, TO))));
 #undef LAUNCH
     return check_launch("attention_generic");
+}
+
+PH_EXPORT int ph_attention_generic(const void* q, int q_dtype, const void* k_base, const void* v_base, int kv_dtype,
+                                   long long page_stride, int page_size, const int32_t* block_table,
+                                   int table_stride, const int32_t* row_seg, const int32_t* positions, void* out,
+                                   int out_dtype, int T, int HQ, int HKV, int D, int window, float scale, int DV,
+                                   int chunk, int v_stride, cudaStream_t stream) {
+    return ph_attention_generic_sink(q, q_dtype, k_base, v_base, kv_dtype, page_stride, page_size, block_table, table_stride, row_seg,
+                                     positions, out, out_dtype, T, HQ, HKV, D, window, scale, DV, chunk, v_stride, nullptr, stream);
 }

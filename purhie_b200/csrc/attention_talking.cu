@@ -1,0 +1,231 @@
+// Attention whose heads talk to each other before the softmax, over cache pages, and the kernel that prepares its
+// queries, keys and values.
+//
+//   joint_norm_kv_write   from the rows [q | k | ...] of one product (partial sums added up): q and k are RMS-normed over
+//                         their whole width (all heads as one row, one weight per element; a null weight: no norm), q
+//                         goes out in the compute dtype, the normed k goes to the key rows of the token's cache slot, and
+//                         the value rows receive k as it was projected, before the norm (values that are the keys), or
+//                         the v part of the row when the product has one.
+//   attention_talking     for the row at position z and every key p that it sees (first_seen(z) <= p <= z):
+//                             s_g = (q_g . k_kv(g)) * scale
+//                             s_g = cap * tanh(s_g / cap)                          (cap > 0)
+//                             s_g = s_g - r1_g * ln(1 + r2_g * (z - p))            (r1, r2 given)
+//                             s'_h = sum_g talk[h][g] * s_g                        (talk given: [HQ, HQ])
+//                         then a softmax over the seen keys per head h (with exp(sink_h) in the denominator when a sink
+//                         is given), o_h = sum_p w_hp v_kv(h)p, and o_h * sigmoid(gate_h) when a gate row is given.
+//                         Because every head's score enters every head's softmax, one block handles all heads of a row:
+//                         warp g scores head g for 32 keys at a time (a key per lane), the block exchanges the scores
+//                         through shared memory, and warp h mixes, runs the online softmax and sums the values of head h.
+// All arithmetic is float32 in an order that depends on (z, window) only, never on how a request was cut into steps or
+// on what else is in the batch.  Cache addressing as in qk_norm_rope.cu.
+#include "common.cuh"
+
+#include <math.h>
+
+namespace {
+
+using namespace ph;
+
+constexpr int MAX_DV = 512;      // widest value row
+constexpr int MAX_HEADS = 32;    // a warp per head, one block per row
+
+template <typename TQ, typename TKV, typename TG, typename TO>
+__global__ void attention_talking_kernel(const TQ* __restrict__ q, const TKV* __restrict__ k_base, const TKV* __restrict__ v_base,
+                                         long long page_stride, int page_size, const int32_t* __restrict__ block_table, int table_stride,
+                                         const int32_t* __restrict__ row_seg, const int32_t* __restrict__ positions,
+                                         TO* __restrict__ out, int HQ, int HKV, int D, int DV, int window, int chunk, float scale,
+                                         float cap, const float* __restrict__ r1, const float* __restrict__ r2,
+                                         const float* __restrict__ talk, const float* __restrict__ sink, const TG* __restrict__ gate,
+                                         long long gate_stride) {
+    extern __shared__ float smem[];
+    float* qs = smem;                          // [HQ][D]
+    float* sc = qs + (size_t)HQ * D;           // [HQ][32]: the heads' own scores of the current 32 keys
+    float* tk = sc + (size_t)HQ * 32;          // [HQ][HQ]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x, h = warp;
+    const int g = h / (HQ / HKV);
+    const int z = positions[t];
+    const int lo = first_seen(z, window, chunk);
+    const int32_t* table = block_table + (size_t)row_seg[t] * table_stride;
+    const TQ* qr = q + (size_t)t * HQ * D;
+    for (int i = threadIdx.x; i < HQ * D; i += blockDim.x) qs[i] = to_float<TQ>(qr[i]);
+    if (talk)
+        for (int i = threadIdx.x; i < HQ * HQ; i += blockDim.x) tk[i] = talk[i];
+    const float b1 = r1 ? r1[h] : 0.0f, b2 = r2 ? r2[h] : 0.0f;
+    __syncthreads();
+
+    float m = -INFINITY, l = 0.0f;
+    float acc[MAX_DV / 32];
+#pragma unroll
+    for (int i = 0; i < MAX_DV / 32; ++i) acc[i] = 0.0f;
+    const float* qh = qs + (size_t)h * D;
+
+    for (int base = lo; base <= z; base += 32) {
+        const int p = base + lane;
+        const bool seen = p <= z;
+        float s = 0.0f;
+        const TKV* vrow = nullptr;
+        if (seen) {
+            const int page = table[p / page_size];
+            const size_t at = (size_t)g * page_size + p % page_size;
+            const TKV* krow = k_base + (size_t)page * page_stride + at * D;
+            vrow = v_base + (size_t)page * page_stride + at * DV;
+            float dot = 0.0f;
+            for (int d = 0; d < D; ++d) dot += qh[d] * to_float<TKV>(krow[d]);
+            s = dot * scale;
+            if (cap > 0.0f) s = cap * tanhf(s / cap);
+            if (r1) s -= b1 * log1pf(b2 * (float)(z - p));
+        }
+        if (talk) {
+            sc[h * 32 + lane] = s;
+            __syncthreads();
+            float mixed = 0.0f;
+            for (int j = 0; j < HQ; ++j) mixed += tk[h * HQ + j] * sc[j * 32 + lane];
+            s = mixed;
+        }
+        if (!seen) s = -INFINITY;
+        const float m_new = fmaxf(m, warp_max(s));
+        const float pexp = seen ? expf(s - m_new) : 0.0f;
+        const float corr = expf(m - m_new);            // m = -inf on the first block: corr = 0, l and acc are 0
+        l = l * corr + warp_sum(pexp);
+#pragma unroll
+        for (int i = 0; i < MAX_DV / 32; ++i) acc[i] *= corr;
+        const int n = (z - base + 1) < 32 ? (z - base + 1) : 32;
+        for (int j = 0; j < n; ++j) {
+            const float pj = __shfl_sync(0xffffffffu, pexp, j);
+            const unsigned long long vp = __shfl_sync(0xffffffffu, (unsigned long long)vrow, j);
+            const TKV* vj = (const TKV*)vp;
+#pragma unroll
+            for (int i = 0; i < MAX_DV / 32; ++i) {
+                const int d = lane + 32 * i;
+                if (d < DV) acc[i] += pj * to_float<TKV>(vj[d]);
+            }
+        }
+        m = m_new;
+        if (talk) __syncthreads();                     // the scores are read before the next block overwrites them
+    }
+    if (sink) {
+        const float sk = sink[h], top = fmaxf(m, sk), corr = expf(m - top);
+        l = l * corr + expf(sk - top);
+#pragma unroll
+        for (int i = 0; i < MAX_DV / 32; ++i) acc[i] *= corr;
+    }
+    TO* o = out + ((size_t)t * HQ + h) * DV;
+    const TG* gr = gate ? gate + (size_t)t * gate_stride + (size_t)h * DV : nullptr;
+    const float inv = 1.0f / l;
+#pragma unroll
+    for (int i = 0; i < MAX_DV / 32; ++i) {
+        const int d = lane + 32 * i;
+        if (d < DV) {
+            float v = acc[i] * inv;
+            if (gr) v *= 1.0f / (1.0f + expf(-to_float<TG>(gr[d])));
+            o[d] = from_float<TO>(v);
+        }
+    }
+}
+
+// One block per token.  The row holds [q (QW) | k (KW) | v (VW, or nothing when the keys are the values) | ...].
+template <typename TI, typename TQ, typename TKV>
+__global__ void joint_norm_kv_write_kernel(const TI* __restrict__ rows, int splits, long long split_stride, long long row_width,
+                                           const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
+                                           const int32_t* __restrict__ slot_mapping, TQ* __restrict__ q_out, TKV* __restrict__ k_base,
+                                           TKV* __restrict__ v_base, long long page_stride, int page_size, int HQ, int HKV, int D, int DV,
+                                           int v_from_row) {
+    extern __shared__ float buf[];             // [QW + KW]
+    __shared__ float scratch[32];
+    const int t = blockIdx.x;
+    const int QW = HQ * D, KW = HKV * D;
+    const TI* src = rows + (size_t)t * row_width;
+    float sq = 0.0f, sk = 0.0f;
+    for (int i = threadIdx.x; i < QW + KW; i += blockDim.x) {
+        float v = 0.0f;
+        for (int s = 0; s < splits; ++s) v += to_float<TI>(src[(size_t)s * split_stride + i]);
+        buf[i] = v;
+        if (i < QW) sq += v * v; else sk += v * v;
+    }
+    const float iq = q_w ? rsqrtf(block_sum_any(sq, scratch) / (float)QW + eps) : 1.0f;
+    const float ik = k_w ? rsqrtf(block_sum_any(sk, scratch) / (float)KW + eps) : 1.0f;
+    __syncthreads();
+    TQ* qo = q_out + (size_t)t * QW;
+    for (int i = threadIdx.x; i < QW; i += blockDim.x) qo[i] = from_float<TQ>(q_w ? buf[i] * iq * q_w[i] : buf[i]);
+    if (!slot_mapping) return;
+    const int slot = slot_mapping[t];
+    if (slot < 0) return;
+    const size_t page_at = (size_t)(slot / page_size) * page_stride;
+    const int off = slot % page_size;
+    for (int i = threadIdx.x; i < KW; i += blockDim.x) {
+        const int h = i / D, d = i % D;
+        const float raw = buf[QW + i];
+        k_base[page_at + ((size_t)h * page_size + off) * D + d] = from_float<TKV>(k_w ? raw * ik * k_w[i] : raw);
+        if (!v_from_row) v_base[page_at + ((size_t)h * page_size + off) * DV + d] = from_float<TKV>(raw);
+    }
+    if (v_from_row) {
+        for (int i = threadIdx.x; i < HKV * DV; i += blockDim.x) {
+            const int h = i / DV, d = i % DV;
+            float v = 0.0f;
+            for (int s = 0; s < splits; ++s) v += to_float<TI>(src[(size_t)s * split_stride + QW + KW + i]);
+            v_base[page_at + ((size_t)h * page_size + off) * DV + d] = from_float<TKV>(v);
+        }
+    }
+}
+
+}  // namespace
+
+// gate: rows of HQ * DV logits, gate_stride elements apart, in gate_dtype (null: no gate).  cap 0: no cap.  r1, r2, talk,
+// sink: float32 per head ([HQ], [HQ], [HQ, HQ], [HQ]) or null.
+PH_EXPORT int ph_attention_talking(const void* q, int q_dtype, const void* k_base, const void* v_base, int kv_dtype, long long page_stride,
+                                   int page_size, const int32_t* block_table, int table_stride, const int32_t* row_seg,
+                                   const int32_t* positions, void* out, int out_dtype, int T, int HQ, int HKV, int D, int DV, int window,
+                                   int chunk, float scale, float cap, const float* r1, const float* r2, const float* talk,
+                                   const float* sink, const void* gate, int gate_dtype, long long gate_stride, cudaStream_t stream) {
+    if (!q || !k_base || !v_base || !block_table || !row_seg || !positions || !out || T < 0 || HQ < 1 || HKV < 1 || D < 1 || DV < 1 ||
+        page_size < 1 || window < 0 || chunk < 0 || !valid_dtype(q_dtype) || !valid_dtype(kv_dtype) || !valid_dtype(out_dtype) ||
+        (gate && !valid_dtype(gate_dtype)) || (r1 == nullptr) != (r2 == nullptr) || cap < 0.0f)
+        return fail(PH_ERR_ARG, "attention_talking: bad arguments (T %d, HQ %d, HKV %d, D %d, DV %d)", T, HQ, HKV, D, DV);
+    if (HQ % HKV) return fail(PH_ERR_ARG, "attention_talking: %d query heads are not a multiple of %d kv heads", HQ, HKV);
+    if (HQ > MAX_HEADS) return fail(PH_ERR_UNSUPPORTED, "attention_talking: %d heads exceed the supported %d", HQ, MAX_HEADS);
+    if (DV > MAX_DV) return fail(PH_ERR_UNSUPPORTED, "attention_talking: value rows of %d exceed the supported %d", DV, MAX_DV);
+    const size_t smem = ((size_t)HQ * D + (size_t)HQ * 32 + (size_t)HQ * HQ) * sizeof(float);
+    if (smem > 200 * 1024) return fail(PH_ERR_UNSUPPORTED, "attention_talking: %d heads of %d do not fit shared memory", HQ, D);
+    if (T == 0) return PH_OK;
+    if (!gate) gate_dtype = q_dtype;
+#define LAUNCH(TQ, TKV, TG, TO)                                                                                                   \
+    do {                                                                                                                          \
+        auto kern = attention_talking_kernel<TQ, TKV, TG, TO>;                                                                    \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                 \
+        kern<<<T, HQ * 32, smem, stream>>>((const TQ*)q, (const TKV*)k_base, (const TKV*)v_base, page_stride, page_size, block_table, \
+                                           table_stride, row_seg, positions, (TO*)out, HQ, HKV, D, DV, window, chunk, scale, cap, \
+                                           r1, r2, talk, sink, (const TG*)gate, gate_stride);                                     \
+    } while (0)
+    PH_DISPATCH(q_dtype, TQ, PH_DISPATCH(kv_dtype, TKV, PH_DISPATCH(gate_dtype, TG, PH_DISPATCH(out_dtype, TO, LAUNCH(TQ, TKV, TG, TO)))));
+#undef LAUNCH
+    return check_launch("attention_talking");
+}
+
+// rows: [splits][T][row_width] in rows_dtype.  q_w [HQ * D] and k_w [HKV * D] float32 or null.  slot_mapping null: no
+// cache write (q only).  v_from_row 0: the values are the keys as projected; 1: the row's third part [HKV * DV].
+PH_EXPORT int ph_joint_norm_kv_write(const void* rows, int rows_dtype, int splits, long long split_stride, long long row_width,
+                                     const float* q_w, const float* k_w, float eps, const int32_t* slot_mapping, void* q_out, int q_dtype,
+                                     void* k_base, void* v_base, int kv_dtype, long long page_stride, int page_size, int T, int HQ,
+                                     int HKV, int D, int DV, int v_from_row, cudaStream_t stream) {
+    if (!rows || !q_out || T < 0 || HQ < 1 || HKV < 1 || D < 1 || DV < 1 || splits < 1 || page_size < 1 || !valid_dtype(rows_dtype) ||
+        !valid_dtype(q_dtype) || !valid_dtype(kv_dtype) || (slot_mapping && (!k_base || !v_base)))
+        return fail(PH_ERR_ARG, "joint_norm_kv_write: bad arguments (T %d, HQ %d, HKV %d, D %d)", T, HQ, HKV, D);
+    if (!v_from_row && DV != D) return fail(PH_ERR_ARG, "joint_norm_kv_write: values that are the keys are as wide as the keys (%d, not %d)", D, DV);
+    const long long need = (long long)(HQ + HKV) * D + (v_from_row ? (long long)HKV * DV : 0);
+    if (row_width < need) return fail(PH_ERR_ARG, "joint_norm_kv_write: rows of %lld elements hold no %lld", row_width, need);
+    const size_t smem = (size_t)(HQ + HKV) * D * sizeof(float);
+    if (smem > 200 * 1024) return fail(PH_ERR_UNSUPPORTED, "joint_norm_kv_write: rows of %d elements do not fit shared memory", (HQ + HKV) * D);
+    if (T == 0) return PH_OK;
+    const int threads = (HQ + HKV) * D >= 2048 ? 512 : 256;
+#define LAUNCH(TI, TQ, TKV)                                                                                                        \
+    do {                                                                                                                           \
+        auto kern = joint_norm_kv_write_kernel<TI, TQ, TKV>;                                                                       \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                  \
+        kern<<<T, threads, smem, stream>>>((const TI*)rows, splits, split_stride, row_width, q_w, k_w, eps, slot_mapping, (TQ*)q_out, \
+                                           (TKV*)k_base, (TKV*)v_base, page_stride, page_size, HQ, HKV, D, DV, v_from_row);        \
+    } while (0)
+    PH_DISPATCH(rows_dtype, TI, PH_DISPATCH(q_dtype, TQ, PH_DISPATCH(kv_dtype, TKV, LAUNCH(TI, TQ, TKV))));
+#undef LAUNCH
+    return check_launch("joint_norm_kv_write");
+}

@@ -30,7 +30,7 @@ LIBRARIES: Dict[str, dict] = {
     "core": {
         "sources": ["elementwise.cu", "qk_norm_rope.cu", "attention_generic.cu", "gemm_simple.cu", "sampling.cu",
                     "random_fill.cu", "layernorm.cu", "gated.cu", "mamba.cu", "moe.cu", "linear_attention.cu", "dyntanh.cu",
-                    "latent_attention.cu", "core_lib.cu"],
+                    "latent_attention.cu", "attention_talking.cu", "min_gru.cu", "core_lib.cu"],
         "deps": ["../weights/random.h"],
         "flags": [],
         "link": [],
@@ -59,7 +59,7 @@ LIBRARIES: Dict[str, dict] = {
                     "../parts/registry.cpp", "../parts/linear.cpp", "../parts/norm.cpp", "../parts/rotary.cpp",
                     "../parts/attention.cpp", "../parts/feed_forward.cpp", "../parts/routed.cpp", "../parts/mamba.cpp",
                     "../parts/linear_attention.cpp", "../parts/latent_attention.cpp", "../parts/embedding.cpp", "../parts/block.cpp",
-                    "../config/bozosun.cpp", "../config/sizizen.cpp", "../config/zerusun.cpp",
+                    "../parts/min_gru.cpp", "../config/bozosun.cpp", "../config/sizizen.cpp", "../config/zerusun.cpp", "../config/vokepel.cpp",
                     "../parts/model.cpp", "../cache/cache.cpp", "../sampling/sampler.cpp", "../engine/engine.cpp",
                     "../engine/scheduler.cpp", "../api/capi.cpp", "../api/capi_generate.cpp", "../api/test_hooks.cpp",
                     "../api/test_hooks_host.cpp", "../api/test_hooks_parts.cpp"],

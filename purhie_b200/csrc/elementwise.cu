@@ -247,7 +247,22 @@ __global__ void cast_kernel(const TI* __restrict__ in, TO* __restrict__ out, lon
     if (i < n) out[i] = from_float<TO>(to_float<TI>(in[i]));
 }
 
+// y = cap * tanh(y * scale / cap) in place (cap 0: y * scale): logits that are scaled and softly capped
+__global__ void scale_softcap_kernel(float* __restrict__ y, long long n, float scale, float cap) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float v = y[i] * scale;
+    y[i] = cap > 0.0f ? cap * tanhf(v / cap) : v;
+}
+
 }  // namespace
+
+PH_EXPORT int ph_scale_softcap(float* y, long long n, float scale, float cap, cudaStream_t stream) {
+    if (!y || n < 0 || cap < 0.0f) return fail(PH_ERR_ARG, "scale_softcap: bad arguments");
+    if (n == 0) return PH_OK;
+    scale_softcap_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(y, n, scale, cap);
+    return check_launch("scale_softcap");
+}
 
 PH_EXPORT int ph_embed_gather(const void* table, int table_dtype, const int32_t* ids, float* out, int T, int E, int V,
                               cudaStream_t stream) {

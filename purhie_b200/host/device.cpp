@@ -178,6 +178,12 @@ const CoreKernels& core_kernels() {
     bind(h, "core", "ph_latent_prepare", g_core.latent_prepare);
     bind(h, "core", "ph_latent_absorb", g_core.latent_absorb);
     bind(h, "core", "ph_latent_expand", g_core.latent_expand);
+    bind(h, "core", "ph_attention_generic_sink", g_core.attention_generic_sink);
+    bind(h, "core", "ph_attention_talking", g_core.attention_talking);
+    bind(h, "core", "ph_joint_norm_kv_write", g_core.joint_norm_kv_write);
+    bind(h, "core", "ph_min_gru_scan", g_core.min_gru_scan);
+    bind(h, "core", "ph_pair_sum", g_core.pair_sum);
+    bind(h, "core", "ph_scale_softcap", g_core.scale_softcap);
     bind(h, "core", "ph_core_last_error", g_core.last_error);
     g_core_ok = true;
     return g_core;

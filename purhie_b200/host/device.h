@@ -154,6 +154,23 @@ struct CoreKernels {
     int (*latent_absorb)(const void*, int, const void*, int, const float*, int, int, const int32_t*, void*, int, int, int, int, int, int,
                          cudaStream_t);
     int (*latent_expand)(const void*, int, const void*, int, const void*, int, long long, void*, int, int, int, int, int, cudaStream_t);
+    // attention with a sink in the softmax's denominator (the plain kernel); attention whose heads' scores are capped,
+    // biased by the distance and mixed before the softmax, with the kernel that norms q and k over their whole width and
+    // writes the cache rows in front of it
+    int (*attention_generic_sink)(const void*, int, const void*, const void*, int, long long, int, const int32_t*, int,
+                                  const int32_t*, const int32_t*, void*, int, int, int, int, int, int, float, int, int, int, const float*,
+                                  cudaStream_t);
+    int (*attention_talking)(const void*, int, const void*, const void*, int, long long, int, const int32_t*, int, const int32_t*,
+                             const int32_t*, void*, int, int, int, int, int, int, int, int, float, float, const float*, const float*,
+                             const float*, const float*, const void*, int, long long, cudaStream_t);
+    int (*joint_norm_kv_write)(const void*, int, int, long long, long long, const float*, const float*, float, const int32_t*, void*, int,
+                               void*, void*, int, long long, int, int, int, int, int, int, int, cudaStream_t);
+    // a minimal gated recurrent unit over the rows of each request; the weighted sum of two mixers' outputs
+    int (*min_gru_scan)(const void*, int, int, long long, long long, const float*, const float*, float*, const int32_t*, const int32_t*,
+                        int, int, int, const int32_t*, int, const int32_t*, float*, void*, int, cudaStream_t);
+    int (*pair_sum)(const void*, int, int, long long, float, const void*, int, int, long long, float, float*, long long, cudaStream_t);
+    // logits scaled and softly capped in place
+    int (*scale_softcap)(float*, long long, float, float, cudaStream_t);
     const char* (*last_error)(void);
 };
 struct FlashKernels {

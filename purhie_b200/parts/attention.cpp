@@ -12,7 +12,8 @@
 // Options of other designs: values of another width than keys ("value_dim"; o_proj then reads num_heads * value_dim),
 // and value mixing across layers ("value_mix": "first" | "blend"): the first such layer of a model leaves its v for
 // every token of the step, the later ones cache and attend over v <- (1 - lambda) v + lambda v_first, with lambda a
-// scalar tensor of their own ("value_mix_factor").
+// scalar tensor of their own ("value_mix_factor"); a sink (names.sink: one float32 number per query head that stands in
+// the softmax's denominator as exp(sink), without a key or a value).
 //
 // K and V are written to pages before attention runs, and attention reads everything, the current step's keys
 // included, from pages: a whole prompt, a portion and a decoded token are one algorithm per kernel.
@@ -132,6 +133,7 @@ public:
         has_norm_ = eps && !eps->is_null();
         eps_ = has_norm_ ? eps->as_double() : 0.0;
         has_bias_ = p.get_bool("bias", false);
+        has_sink_ = names_.count("sink") != 0;
         window_ = (int)p.get_int("window", 0);
         chunk_ = (int)p.get_int("chunk", 0);
         if (chunk_ < 0) throw ConfigError("attention: a block mask holds at least one position");
@@ -162,6 +164,7 @@ public:
                                      {name_of("v_proj"), {v_width_, hidden_}, Role::Matrix, Init::Normal},
                                      {name_of("o_proj"), {hidden_, o_width_}, Role::Matrix, Init::Normal}};
         if (value_mix_ == 2) s.push_back({name_of("value_mix_factor"), {}, Role::Vector, Init::Normal});
+        if (has_sink_) s.push_back({name_of("sink"), {heads_}, Role::Vector, Init::Normal});
         if (has_norm_) {
             s.push_back({name_of("q_norm"), {head_dim_}, Role::Vector, Init::Scale});
             s.push_back({name_of("k_norm"), {head_dim_}, Role::Vector, Init::Scale});
@@ -206,6 +209,7 @@ public:
             k_norm_ = src.fetch(name_of("k_norm"));
         }
         if (value_mix_ == 2) mix_factor_ = src.fetch(name_of("value_mix_factor"));
+        if (has_sink_) sink_ = src.fetch(name_of("sink"));
         if (position_) {
             position_->bind(src);
             table_ = position_->rotation_table();
@@ -233,7 +237,8 @@ public:
     bool use_flash() const {
         if (compute_dtype != DType::BF16 || attention_ == "generic") return false;
         const int group = heads_ / kv_heads_;
-        const bool ok = (head_dim_ == 64 || head_dim_ == 128) && value_dim_ == head_dim_ && group >= 1 && group <= 16;
+        // (the tensor-core kernels know no sink)
+        const bool ok = (head_dim_ == 64 || head_dim_ == 128) && value_dim_ == head_dim_ && group >= 1 && group <= 16 && !has_sink_;
         if (!ok && attention_ == "flash")
             throw KernelError("the flash attention kernels do not take head_dim " + std::to_string(head_dim_) + " with " +
                               std::to_string(group) + " query heads per kv head");
@@ -317,10 +322,10 @@ public:
             if (cache.kv_dtype != DType::BF16) throw KernelError("attention_flash: the cache must be bfloat16");
             flash(q, cache, g, ctx, out, abs_positions);
         } else {
-            QE_LAUNCH(core, core.attention_generic(q.data, q.code(), cache.k_base, cache.v_base, (int)cache.kv_dtype, cache.page_stride,
-                                                   cache.page_size, g.block_table, g.table_width, ctx.row_seg, abs_positions, out.data,
-                                                   out.code(), T, heads_, kv_heads_, head_dim_, window_, (float)scale_, value_dim_, chunk_, 0,
-                                                   ctx.stream));
+            QE_LAUNCH(core, core.attention_generic_sink(q.data, q.code(), cache.k_base, cache.v_base, (int)cache.kv_dtype, cache.page_stride,
+                                                        cache.page_size, g.block_table, g.table_width, ctx.row_seg, abs_positions, out.data,
+                                                        out.code(), T, heads_, kv_heads_, head_dim_, window_, (float)scale_, value_dim_, chunk_, 0,
+                                                        has_sink_ ? sink_.as<float>() : nullptr, ctx.stream));
         }
         return o_proj_(out, ctx, "o_out", DType::F32, T, true, false, ctx.residual, nullptr, &ctx.norm_ahead);
     }
@@ -376,16 +381,183 @@ private:
 
     int64_t hidden_, q_width_, kv_width_, v_width_, o_width_;
     int heads_, kv_heads_, head_dim_, value_dim_, window_, chunk_ = 0, value_mix_ = 0;
-    bool has_norm_, has_bias_;
+    bool has_norm_, has_bias_, has_sink_ = false;
     double eps_, scale_;
     std::string gemm_, attention_;
     std::shared_ptr<PositionEncoding> position_;
     Linear qkv_proj_, q_only_proj_, o_proj_;
-    Tensor q_norm_, k_norm_, bias_, table_, mix_factor_;
+    Tensor q_norm_, k_norm_, bias_, table_, mix_factor_, sink_;
+};
+
+// Grouped-query attention whose heads talk to each other before the softmax.
+//
+//   q = Wq h, k = Wk h; q and k are RMS-normed over their whole width (all heads as one row, a weight per element;
+//   "joint_norm_eps" null: no norm); v = Wv h, or, with "values": "keys", the keys as projected, before their norm (the
+//   mixer then has no Wv).  No rotation.  For the row at position z and a key at p:
+//       s_g = (q_g . k_kv(g)) * scale;   s_g <- cap * tanh(s_g / cap)   ("softcap" null: no cap);
+//       s_g <- s_g - r1_g ln(1 + r2_g (z - p))   (names.distance_slope and names.distance_rate, both or none);
+//       s_h <- sum_g talk[h, g] s_g              (names.head_mix, [heads, heads]; absent: the heads stay apart);
+//   softmax over the last `window` positions (null: all), with exp(sink_h) in the denominator when names.sink is given;
+//   the heads side by side times sigmoid(Wg h) (names.gate_proj; absent: no gate); y = Wo o.
+// The projections of h are one product over the stacked matrices [q | k | (v) | (g)].  The normed keys and the values go
+// into the request's pages before attention runs, and attention reads everything from pages, so a whole prompt, a
+// portion and a decoded token are one algorithm.  Scores, the cap, the bias, the mix and the softmax are float32 in
+// every mode.
+// params: hidden_size, num_heads, num_kv_heads, head_dim, value_dim (null: head_dim), values ("projection" | "keys"),
+// joint_norm_eps, window, scale (null: 1/sqrt(head_dim)), softcap,
+// names{q_proj, k_proj, v_proj, o_proj, q_norm, k_norm, distance_slope, distance_rate, head_mix, sink, gate_proj}.
+class TalkingAttention : public Mixer {
+public:
+    TalkingAttention(const Json& p, BuildContext& b) : Mixer(p, b) {
+        hidden_ = p.at("hidden_size").as_int();
+        heads_ = (int)p.at("num_heads").as_int();
+        kv_heads_ = (int)p.at("num_kv_heads").as_int();
+        head_dim_ = (int)p.at("head_dim").as_int();
+        value_dim_ = (int)p.get_int("value_dim", head_dim_);
+        if (heads_ < 1 || kv_heads_ < 1 || heads_ % kv_heads_)
+            throw ConfigError(std::to_string(heads_) + " query heads are not a multiple of " + std::to_string(kv_heads_) + " kv heads");
+        if (head_dim_ < 1 || value_dim_ < 1) throw ConfigError("talking_attention: head_dim and value_dim must be positive");
+        const std::string values = p.get_string("values", "projection");
+        if (values != "projection" && values != "keys") throw ConfigError("talking_attention: values is 'projection' or 'keys', got '" + values + "'");
+        values_are_keys_ = values == "keys";
+        if (values_are_keys_ && value_dim_ != head_dim_)
+            throw ConfigError("talking_attention: values that are the keys are " + std::to_string(head_dim_) + " wide, not " + std::to_string(value_dim_));
+        const Json* eps = p.find("joint_norm_eps");
+        has_norm_ = eps && !eps->is_null();
+        eps_ = has_norm_ ? eps->as_double() : 0.0;
+        window_ = (int)p.get_int("window", 0);
+        const Json* sc = p.find("scale");
+        scale_ = (sc && !sc->is_null()) ? sc->as_double() : 1.0 / std::sqrt((double)head_dim_);
+        const Json* cap = p.find("softcap");
+        softcap_ = (cap && !cap->is_null()) ? cap->as_double() : 0.0;
+        if (softcap_ < 0.0) throw ConfigError("talking_attention: softcap must be positive");
+        has_distance_ = names_.count("distance_slope") != 0;
+        if (has_distance_ != (names_.count("distance_rate") != 0)) throw ConfigError("talking_attention: the distance bias needs both distance_slope and distance_rate");
+        has_mix_ = names_.count("head_mix") != 0;
+        has_sink_ = names_.count("sink") != 0;
+        has_gate_ = names_.count("gate_proj") != 0;
+        gemm_ = b.options.get_string("gemm", "auto");
+        q_width_ = (int64_t)heads_ * head_dim_;
+        kv_width_ = (int64_t)kv_heads_ * head_dim_;
+        v_width_ = values_are_keys_ ? 0 : (int64_t)kv_heads_ * value_dim_;
+        o_width_ = (int64_t)heads_ * value_dim_;
+        g_width_ = has_gate_ ? o_width_ : 0;
+    }
+
+    std::vector<TensorSpec> tensor_specs() const override {
+        std::vector<TensorSpec> s = {{name_of("q_proj"), {q_width_, hidden_}, Role::Matrix, Init::Normal},
+                                     {name_of("k_proj"), {kv_width_, hidden_}, Role::Matrix, Init::Normal},
+                                     {name_of("o_proj"), {hidden_, o_width_}, Role::Matrix, Init::Normal}};
+        if (!values_are_keys_) s.push_back({name_of("v_proj"), {v_width_, hidden_}, Role::Matrix, Init::Normal});
+        if (has_gate_) s.push_back({name_of("gate_proj"), {g_width_, hidden_}, Role::Matrix, Init::Normal});
+        if (has_norm_) {
+            s.push_back({name_of("q_norm"), {q_width_}, Role::Vector, Init::Scale});
+            s.push_back({name_of("k_norm"), {kv_width_}, Role::Vector, Init::Scale});
+        }
+        if (has_distance_) {
+            s.push_back({name_of("distance_slope"), {heads_}, Role::Vector, Init::Normal});
+            s.push_back({name_of("distance_rate"), {heads_}, Role::Vector, Init::Scale});
+        }
+        if (has_mix_) s.push_back({name_of("head_mix"), {heads_, heads_}, Role::Vector, Init::Normal});
+        if (has_sink_) s.push_back({name_of("sink"), {heads_}, Role::Vector, Init::Normal});
+        return s;
+    }
+
+    void bind(WeightSource& src) override {
+        // one matrix [q | k | (v) | (g)] so that the projections of h are one product (a layout choice only)
+        std::vector<Tensor> parts = {src.fetch(name_of("q_proj")), src.fetch(name_of("k_proj"))};
+        if (!values_are_keys_) parts.push_back(src.fetch(name_of("v_proj")));
+        if (has_gate_) parts.push_back(src.fetch(name_of("gate_proj")));
+        for (Tensor& t : parts)
+            if (t.dtype != parts[0].dtype) throw WeightError("the projections of " + name_of("q_proj") + "'s mixer are stored in different precisions");
+        Tensor all = src.arena().alloc(parts[0].dtype, {q_width_ + kv_width_ + v_width_ + g_width_, hidden_});
+        size_t off = 0;
+        for (Tensor& t : parts) {
+            QE_CUDA(cudaMemcpyAsync(static_cast<char*>(all.data) + off, t.data, t.bytes(), cudaMemcpyDeviceToDevice, src.stream()));
+            off += t.bytes();
+        }
+        QE_CUDA(cudaStreamSynchronize(src.stream()));
+        for (Tensor& t : parts) src.release(t);
+        in_proj_ = Linear(all, "qkvg_proj", gemm_);
+        o_proj_ = Linear(src.fetch(name_of("o_proj")), "o_proj", gemm_);
+        if (has_norm_) {
+            q_norm_ = src.fetch(name_of("q_norm"));
+            k_norm_ = src.fetch(name_of("k_norm"));
+        }
+        if (has_distance_) {
+            slope_ = src.fetch(name_of("distance_slope"));
+            rate_ = src.fetch(name_of("distance_rate"));
+        }
+        if (has_mix_) mix_ = src.fetch(name_of("head_mix"));
+        if (has_sink_) sink_ = src.fetch(name_of("sink"));
+    }
+
+    std::vector<std::string> required_libraries() const override {
+        return (in_proj_.fast() || o_proj_.fast()) ? std::vector<std::string>{"core", "gemm100"} : std::vector<std::string>{"core"};
+    }
+    int preferred_row_multiple() const override { return (in_proj_.fast() || o_proj_.fast()) ? 256 : 0; }
+    CacheNeed cache_need() const override { return CacheNeed::pages(kv_heads_, head_dim_, window_, value_dim_); }
+
+    Addend forward(const Tensor& x, StepContext& ctx, const CacheView& cache) override {
+        if (!cache.writable) throw Error(kInvalidState, "talking_attention writes a cache of its own");
+        const int T = ctx.T;
+        Workspace& ws = *ctx.workspace;
+        const DType dt = compute_dtype;
+        const GroupStep& g = ctx.groups.at(cache.group);
+        const CoreKernels& core = core_kernels();
+        const int64_t width = q_width_ + kv_width_ + v_width_ + g_width_;
+        Addend in = in_proj_(x, ctx, "talk_in", dt, T, !has_gate_);
+        Tensor q = ws.get("talk_q", {T, heads_, head_dim_}, dt);
+        const size_t in_size = dtype_size(in.tensor.dtype);
+        if (LaunchProfile::get().on())
+            LaunchProfile::get().note_cost((double)T * ((q_width_ + kv_width_ + v_width_) * (double)in.splits * in_size +
+                                                        (q_width_ + kv_width_ + (double)kv_heads_ * value_dim_) * dtype_size(dt)), 0.0);
+        QE_LAUNCH(core, core.joint_norm_kv_write(in.tensor.data, in.tensor.code(), in.splits, (long long)T * width, width,
+                                                 has_norm_ ? q_norm_.as<float>() : nullptr, has_norm_ ? k_norm_.as<float>() : nullptr, (float)eps_,
+                                                 g.slot_mapping, q.data, q.code(), cache.k_base, cache.v_base, (int)cache.kv_dtype, cache.page_stride,
+                                                 cache.page_size, T, heads_, kv_heads_, head_dim_, value_dim_, values_are_keys_ ? 0 : 1, ctx.stream));
+        // the gate's logits stay where the product left them (a product that feeds a gate keeps K whole)
+        const void* gate = nullptr;
+        if (has_gate_) {
+            if (in.splits != 1) throw Error(kInvalidState, "talking_attention: the gate's logits came as partial sums");
+            gate = static_cast<const char*>(in.tensor.data) + (q_width_ + kv_width_ + v_width_) * in_size;
+        }
+        const int gate_code = in.tensor.code();
+        const long long gate_stride = width;
+        Tensor out = ws.get("talk_out", {T, o_width_}, dt);
+        if (LaunchProfile::get().on()) {
+            double seen = 0.0, read = 0.0;
+            for (size_t i = 0; i < ctx.q_lens.size(); i++) {
+                const double n = ctx.q_lens[i], len = ctx.ctx_lens[i];
+                read += window_ ? std::min<double>(len, window_ + n) : len;
+                seen += window_ ? n * std::min<double>(len, window_) : n * (len - n) + n * (n + 1) / 2.0;
+            }
+            LaunchProfile::get().note_cost(read * kv_heads_ * (head_dim_ + value_dim_) * dtype_size(cache.kv_dtype) +
+                                               (double)T * (q_width_ + o_width_ + g_width_) * dtype_size(dt),
+                                           2.0 * seen * heads_ * (head_dim_ + value_dim_ + (has_mix_ ? heads_ : 0)));
+        }
+        QE_LAUNCH(core, core.attention_talking(q.data, q.code(), cache.k_base, cache.v_base, (int)cache.kv_dtype, cache.page_stride, cache.page_size,
+                                               g.block_table, g.table_width, ctx.row_seg, ctx.position_column(0), out.data, out.code(), T, heads_,
+                                               kv_heads_, head_dim_, value_dim_, window_, 0, (float)scale_, (float)softcap_,
+                                               has_distance_ ? slope_.as<float>() : nullptr, has_distance_ ? rate_.as<float>() : nullptr,
+                                               has_mix_ ? mix_.as<float>() : nullptr, has_sink_ ? sink_.as<float>() : nullptr, gate, gate_code,
+                                               gate_stride, ctx.stream));
+        return o_proj_(out, ctx, "talk_o", DType::F32, T, true, false, ctx.residual, nullptr, &ctx.norm_ahead);
+    }
+
+private:
+    int64_t hidden_, q_width_, kv_width_, v_width_, o_width_, g_width_;
+    int heads_, kv_heads_, head_dim_, value_dim_, window_;
+    bool values_are_keys_, has_norm_, has_distance_, has_mix_, has_sink_, has_gate_;
+    double eps_, scale_, softcap_;
+    std::string gemm_;
+    Linear in_proj_, o_proj_;
+    Tensor q_norm_, k_norm_, slope_, rate_, mix_, sink_;
 };
 
 void register_mixer_parts() {
     register_part("mixer", "attention", [](const Json& p, BuildContext& b) { return std::make_shared<Attention>(p, b); });
+    register_part("mixer", "talking_attention", [](const Json& p, BuildContext& b) { return std::make_shared<TalkingAttention>(p, b); });
 }
 
 }  // namespace qe

@@ -2,7 +2,9 @@
 //
 // pre_norm: x += mixer(norm1(x)); x += feed_forward(norm2(x)), with each addition folded into the norm that
 // follows it (the reference fuses them the same way: src/qwen_model.cpp:1175-1187, 1248, 1260).  Sub-parts by
-// name: mixer_norm, mixer, feed_forward_norm, feed_forward.
+// name: mixer_norm, mixer, feed_forward_norm, feed_forward (a layer may come without the last two).  With the layer
+// param "residual_factor" m != 1 the layer is x += m * mixer(norm1(x)); x += m * feed_forward(norm2(x)): the factor
+// travels with each part's addend as its transform, and whoever folds the addend in applies it.
 //
 // sandwich_norm: x += m * post_norm(mixer(norm1(x))); x += m * post_norm2(feed_forward(norm2(x))), a norm in front of
 // and behind each part and a factor m on what is added (layer param "residual_factor", default 1).  The norm behind
@@ -29,12 +31,20 @@ public:
     PreNormBlock(const LayerSpec& layer, BuildContext& build) {
         mixer_norm_ = make_part_as<Norm>("norm", layer.part("mixer_norm"), build);
         mixer_ = make_part_as<Mixer>("mixer", layer.part("mixer"), build);
-        ff_norm_ = make_part_as<Norm>("norm", layer.part("feed_forward_norm"), build);
-        ff_ = make_part_as<FeedForward>("feed_forward", layer.part("feed_forward"), build);
+        if (layer.has("feed_forward")) {
+            ff_norm_ = make_part_as<Norm>("norm", layer.part("feed_forward_norm"), build);
+            ff_ = make_part_as<FeedForward>("feed_forward", layer.part("feed_forward"), build);
+        }
+        factor_ = (float)layer.params.get_double("residual_factor", 1.0);
     }
-    std::vector<Part*> parts() override { return {mixer_norm_.get(), mixer_.get(), ff_norm_.get(), ff_.get()}; }
+    std::vector<Part*> parts() override {
+        std::vector<Part*> p = {mixer_norm_.get(), mixer_.get()};
+        if (ff_) { p.push_back(ff_norm_.get()); p.push_back(ff_.get()); }
+        return p;
+    }
     CacheNeed cache_need() const override { return mixer_->cache_need(); }
     void forward(ResidualStream& stream, StepContext& ctx, const CacheView& cache) override {
+        if (factor_ != 1.0f) return forward_scaled(stream, ctx, cache);
         ctx.residual = stream.x.as<float>();
         ctx.residual_width = stream.x.shape[1];
         // a consumer that applies the row's factor itself lets the norm in front leave it out (RowScale)
@@ -43,14 +53,15 @@ public:
         // and a part whose last product adds into the residual itself may do the pass of the norm behind it there
         // (NormAhead; the option "norm_ahead": "off" keeps every norm a kernel of its own)
         const bool may_work_ahead = may_defer && ctx.option("norm_ahead") != "off";
-        const bool ff_unscaled = may_defer && ff_->takes_unscaled_rows(ctx);
+        const bool ff_unscaled = ff_ && may_defer && ff_->takes_unscaled_rows(ctx);
         ctx.row_scale = RowScale();
         Tensor xn = may_defer && mixer_->takes_unscaled_rows(ctx) ? mixer_norm_->forward_unscaled(stream, ctx, &ctx.row_scale)
                                                                   : mixer_norm_->forward(stream, ctx);
-        ctx.norm_ahead = may_work_ahead && ff_unscaled ? ff_norm_->offer(ctx) : NormAhead();
+        ctx.norm_ahead = may_work_ahead && ff_unscaled ? ff_norm_->offer(ctx) : (!ff_ && may_work_ahead) ? ctx.next_layer_norm : NormAhead();
         stream.add(mixer_->forward(xn, ctx, cache));
         stream.prepare(ctx.norm_ahead);
         ctx.row_scale = RowScale();
+        if (!ff_) { ctx.norm_ahead = NormAhead(); return; }
         xn = ff_unscaled ? ff_norm_->forward_unscaled(stream, ctx, &ctx.row_scale) : ff_norm_->forward(stream, ctx);
         ctx.norm_ahead = may_work_ahead ? ctx.next_layer_norm : NormAhead();
         stream.add(ff_->forward(xn, ctx));
@@ -60,9 +71,29 @@ public:
     }
     NormAhead first_norm(const StepContext& ctx) const override {
         const bool may_defer = ctx.option("row_factor") != "norm";
-        return may_defer && mixer_->takes_unscaled_rows(ctx) ? mixer_norm_->offer(ctx) : NormAhead();
+        return factor_ == 1.0f && may_defer && mixer_->takes_unscaled_rows(ctx) ? mixer_norm_->offer(ctx) : NormAhead();
     }
 private:
+    // What a part gives is multiplied by the factor on its way into the residual, so no product adds into the residual
+    // itself and no norm's work is handed to a product: every part returns its addend, which carries the factor.
+    void forward_scaled(ResidualStream& stream, StepContext& ctx, const CacheView& cache) {
+        ctx.residual = nullptr;
+        ctx.residual_width = 0;
+        ctx.row_scale = RowScale();
+        ctx.norm_ahead = NormAhead();
+        Tensor xn = mixer_norm_->forward(stream, ctx);
+        Addend mixed = mixer_->forward(xn, ctx, cache);
+        if (!mixed.tensor.defined()) throw Error(kInvalidState, "pre_norm: the mixer added into the residual itself");
+        mixed.transform.factor *= factor_;
+        stream.add(std::move(mixed));
+        if (!ff_) return;
+        xn = ff_norm_->forward(stream, ctx);
+        Addend fed = ff_->forward(xn, ctx);
+        if (!fed.tensor.defined()) throw Error(kInvalidState, "pre_norm: the feed-forward added into the residual itself");
+        fed.transform.factor *= factor_;
+        stream.add(std::move(fed));
+    }
+    float factor_ = 1.0f;
     std::shared_ptr<Norm> mixer_norm_, ff_norm_;
     std::shared_ptr<Mixer> mixer_;
     std::shared_ptr<FeedForward> ff_;
@@ -209,6 +240,7 @@ void register_norm_parts();
 void register_routed_parts();
 void register_state_space_parts();
 void register_linear_attention_parts();
+void register_recurrent_parts();
 void register_latent_attention_parts();
 void register_position_parts();
 void register_mixer_parts();
@@ -227,6 +259,7 @@ void register_builtin_parts() {
     register_routed_parts();
     register_state_space_parts();
     register_linear_attention_parts();
+    register_recurrent_parts();
     register_latent_attention_parts();
     register_arrangement("sandwich_norm", [](const LayerSpec& layer, BuildContext& build) {
         return std::unique_ptr<Arrangement>(new SandwichNormBlock(layer, build));

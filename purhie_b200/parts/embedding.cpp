@@ -42,11 +42,16 @@ private:
 };
 
 // params: hidden_size, vocab_size, and either names{weight} or tied_to (a tensor another part reads); ignore: names
-// that may be present in a checkpoint and are not read (a stray lm_head.weight beside a tied head).
+// that may be present in a checkpoint and are not read (a stray lm_head.weight beside a tied head); scale (default 1)
+// and softcap (null: none): logits <- softcap * tanh(logits * scale / softcap), in float32.
 class LMHead : public Head {
 public:
     LMHead(const Json& p, BuildContext& b) : Head(p, b), hidden_(p.at("hidden_size").as_int()), vocab_(p.at("vocab_size").as_int()) {
         tied_to_ = p.get_string("tied_to", "");
+        scale_ = p.get_double("scale", 1.0);
+        if (const Json* cap = p.find("softcap"))
+            if (!cap->is_null()) softcap_ = cap->as_double();
+        if (softcap_ < 0.0) throw ConfigError("lm_head: softcap must be positive");
         if (const Json* ig = p.find("ignore"))
             for (const Json& n : ig->items()) ignore_.push_back(n.as_string());
         gemm_ = b.options.get_string("gemm", "auto");
@@ -59,10 +64,17 @@ public:
     void bind(WeightSource& src) override { proj_ = Linear(src.fetch(tied_to_.empty() ? name_of("weight") : tied_to_), "lm_head", gemm_); }
     std::vector<std::string> required_libraries() const override { return proj_.defined() ? proj_.required_libraries() : std::vector<std::string>{"core"}; }
     Tensor forward(const Tensor& xn, StepContext& ctx, int n_rows) override {
-        return proj_(xn, ctx, "logits", DType::F32, n_rows).tensor;
+        Tensor logits = proj_(xn, ctx, "logits", DType::F32, n_rows).tensor;
+        if (scale_ != 1.0 || softcap_ > 0.0) {
+            const CoreKernels& k = core_kernels();
+            if (LaunchProfile::get().on()) LaunchProfile::get().note_cost(8.0 * n_rows * vocab_, 0.0);
+            QE_LAUNCH(k, k.scale_softcap(logits.as<float>(), (long long)n_rows * vocab_, (float)scale_, (float)softcap_, ctx.stream));
+        }
+        return logits;
     }
 private:
     int64_t hidden_, vocab_;
+    double scale_ = 1.0, softcap_ = 0.0;
     std::string tied_to_, gemm_;
     std::vector<std::string> ignore_;
     Linear proj_;

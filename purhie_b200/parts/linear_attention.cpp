@@ -17,7 +17,8 @@
 // lists with gated_linear_attention; the norm over the whole row and the gate are a kernel behind it.
 //
 // side_by_side: y = factor * (rmsnorm(left(h); w_left) + rmsnorm(right(h); w_right)), both norms over the model
-// width.  "left" and "right" are mixers of any registered kind, given as {kind, params}; one of them may keep pages
+// width; or, with "combine": "weighted_sum", y = left_factor * left(h) + right_factor * right(h) without norms (and
+// without norm tensors).  "left" and "right" are mixers of any registered kind, given as {kind, params}; one of them may keep pages
 // and one a state (CacheNeed::both), and each finds what it keeps in the layer's cache view.
 #include <algorithm>
 #include <cmath>
@@ -276,23 +277,35 @@ private:
     Tensor decay_, norm_;
 };
 
-// params: hidden_size, eps, factor (default 0.5), left {kind, params}, right {kind, params}, names{left_norm, right_norm}.
+// params: hidden_size, left {kind, params}, right {kind, params}, combine ("rms_mean", the default: eps, factor (default
+// 0.5), names{left_norm, right_norm}; "weighted_sum": left_factor, right_factor).
 class SideBySide : public Mixer {
 public:
     SideBySide(const Json& p, BuildContext& b) : Mixer(p, b) {
         hidden_ = p.at("hidden_size").as_int();
-        eps_ = p.at("eps").as_double();
-        factor_ = p.get_double("factor", 0.5);
+        const std::string combine = p.get_string("combine", "rms_mean");
+        if (combine != "rms_mean" && combine != "weighted_sum") throw ConfigError("side_by_side: combine is 'rms_mean' or 'weighted_sum', got '" + combine + "'");
+        weighted_ = combine == "weighted_sum";
+        if (weighted_) {
+            left_factor_ = p.at("left_factor").as_double();
+            right_factor_ = p.at("right_factor").as_double();
+        } else {
+            eps_ = p.at("eps").as_double();
+            factor_ = p.get_double("factor", 0.5);
+        }
         left_ = make_part_as<Mixer>("mixer", PartSpec::from_json(p.at("left")), b);
         right_ = make_part_as<Mixer>("mixer", PartSpec::from_json(p.at("right")), b);
         CacheNeed::both(left_->cache_need(), right_->cache_need());          // throws when the two cannot share a layer's cache
     }
     std::vector<TensorSpec> tensor_specs() const override {
+        if (weighted_) return {};
         return {{name_of("left_norm"), {hidden_}, Role::Vector, Init::Scale}, {name_of("right_norm"), {hidden_}, Role::Vector, Init::Scale}};
     }
     void bind(WeightSource& src) override {
-        left_w_ = src.fetch(name_of("left_norm"));
-        right_w_ = src.fetch(name_of("right_norm"));
+        if (!weighted_) {
+            left_w_ = src.fetch(name_of("left_norm"));
+            right_w_ = src.fetch(name_of("right_norm"));
+        }
         left_->bind(src);
         right_->bind(src);
     }
@@ -334,15 +347,21 @@ public:
         const CoreKernels& k = core_kernels();
         if (LaunchProfile::get().on())
             LaunchProfile::get().note_cost((double)T * hidden_ * (a.splits * dtype_size(a.tensor.dtype) + b.splits * dtype_size(b.tensor.dtype) + 4.0), 0.0);
-        QE_LAUNCH(k, k.rms_pair_mean(a.tensor.data, a.tensor.code(), a.splits, (long long)T * hidden_, left_w_.as<float>(), b.tensor.data,
-                                     b.tensor.code(), b.splits, (long long)T * hidden_, right_w_.as<float>(), (float)eps_, (float)factor_,
-                                     out.as<float>(), T, (int)hidden_, ctx.stream));
+        if (weighted_)
+            QE_LAUNCH(k, k.pair_sum(a.tensor.data, a.tensor.code(), a.splits, (long long)T * hidden_, (float)left_factor_, b.tensor.data,
+                                    b.tensor.code(), b.splits, (long long)T * hidden_, (float)right_factor_, out.as<float>(),
+                                    (long long)T * hidden_, ctx.stream));
+        else
+            QE_LAUNCH(k, k.rms_pair_mean(a.tensor.data, a.tensor.code(), a.splits, (long long)T * hidden_, left_w_.as<float>(), b.tensor.data,
+                                         b.tensor.code(), b.splits, (long long)T * hidden_, right_w_.as<float>(), (float)eps_, (float)factor_,
+                                         out.as<float>(), T, (int)hidden_, ctx.stream));
         return Addend(out, 1);
     }
 
 private:
     int64_t hidden_;
-    double eps_, factor_;
+    bool weighted_ = false;
+    double eps_ = 0.0, factor_ = 0.5, left_factor_ = 1.0, right_factor_ = 1.0;
     std::shared_ptr<Mixer> left_, right_;
     Tensor left_w_, right_w_;
 };

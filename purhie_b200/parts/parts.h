@@ -436,8 +436,8 @@ template <typename T> std::shared_ptr<T> make_part_as(const std::string& family,
     return p;
 }
 
-// Registers the parts this library brings (rmsnorm, layernorm, none, dyntanh, rope_neox, attention, latent_attention,
-// mamba1, gated_linear_attention, lightning_attention, side_by_side, swiglu, mlp, routed_glu, embedding, lm_head,
+// Registers the parts this library brings (rmsnorm, layernorm, none, dyntanh, rope_neox, attention, talking_attention,
+// latent_attention, mamba1, gated_linear_attention, lightning_attention, min_gru, side_by_side, swiglu, mlp, routed_glu, embedding, lm_head,
 // pre_norm, sandwich_norm, parallel, reinject).
 QE_API void register_builtin_parts();
 
