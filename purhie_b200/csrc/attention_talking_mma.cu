@@ -1,0 +1,242 @@
+// Attention whose heads talk to each other before the softmax, on the tensor cores (bfloat16 in, float32 scores, cap,
+// bias, mix, softmax and sums): the many-row and the few-row form of attention_talking (attention_talking.cu states the
+// equations).  It also serves attention that only has a sink, or only a gate: every extra is optional.
+//
+// One CTA per tile of 16 query rows of one request (a decode row is a tile of one row) and ALL heads, a warp per head:
+// every head's score at a (row, key) pair enters every head's softmax, so the heads of a tile must meet.  Keys are walked
+// in blocks of 32 from the first one the tile sees to its last row's position.  Per block the CTA gathers the keys and
+// values of all kv heads from the pages into shared memory (16-byte cp.async, rows outside the visible range zero-filled,
+// so whatever an unwritten or reused page holds never reaches a product); warp h computes S_h = Q_h K_kv(h)^T with
+// mma.sync.m16n8k16, scales, caps and biases it in float32 and leaves it in shared memory; after a barrier it reads all
+// heads' scores at its own (row, key) places and mixes them with its row of the talk matrix; then the online softmax
+// (running maximum and sum per row) and O_h += P_h V_kv(h) on the tensor cores with P rounded to bfloat16, as in the
+// other tensor-core attention kernels.  The sink joins the denominator at the end; the gate multiplies the output.
+// Q tiles of all heads pass through the shared memory that the keys use afterwards.
+#include "attention_mma.cuh"
+
+namespace {
+
+using namespace ph;
+using namespace ph_attn;
+
+constexpr int BM = 16;            // query rows of a tile
+constexpr int BK = 32;            // keys of a block
+constexpr int SP = 40;            // floats between two rows of the exchanged scores (8-byte accesses miss each other's banks)
+constexpr int MAX_HEADS = 16;      // a warp per head, and a thread keeps its head's Q and O in registers
+
+struct TalkParams {
+    const __nv_bfloat16* q; const __nv_bfloat16* k_base; const __nv_bfloat16* v_base;
+    long long page_stride; int page_size;
+    const int32_t* block_table; int table_stride;
+    const int32_t* seg_start; const int32_t* seg_ctx_len; const int32_t* tile_seg; const int32_t* tile_first;
+    __nv_bfloat16* out;
+    int HQ, HKV, window, chunk;
+    float scale, cap;
+    const float* r1; const float* r2; const float* talk; const float* sink;
+    const __nv_bfloat16* gate; long long gate_stride;
+    int kv_bytes;                 // bytes of the region that holds Q first and the blocks of K and V afterwards
+};
+
+template <int D, int DV>
+__global__ void __launch_bounds__(MAX_HEADS * 32) attention_talking_mma_kernel(const TalkParams p) {
+    constexpr int KP = D * 2 + 16, VP = DV * 2 + 16;          // bytes between two rows of a K (Q) and of a V tile
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int HQ = p.HQ, HKV = p.HKV;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, threads = blockDim.x;
+    const int h = warp, g = h / (HQ / HKV);
+    const uint32_t region = smem_u32(smem);
+    float* sc = reinterpret_cast<float*>(smem + p.kv_bytes);  // [HQ][BM][SP]
+    float* tk = sc + (size_t)HQ * BM * SP;                    // [HQ][HQ]
+
+    const int tile = blockIdx.x;
+    const int seg = p.tile_seg[tile], first = p.tile_first[tile];
+    const int row0 = p.seg_start[seg], q_len = p.seg_start[seg + 1] - row0;
+    const int ctx_len = p.seg_ctx_len[seg];
+    const int n_rows = min(BM, q_len - first);
+    const int z_first = ctx_len - q_len + first, z_last = z_first + n_rows - 1;
+    const int32_t* table = p.block_table + (size_t)seg * p.table_stride;
+
+    // Q of all heads: [HQ][BM] rows of D; rows beyond the portion are zero
+    {
+        constexpr int CPR = D / 8;
+        for (int i = threadIdx.x; i < HQ * BM * CPR; i += threads) {
+            const int c = i % CPR, r = (i / CPR) % BM, hh = i / (CPR * BM);
+            const bool valid = r < n_rows;
+            const __nv_bfloat16* src = p.q + ((size_t)(row0 + first + (valid ? r : 0)) * HQ + hh) * D + c * 8;
+            cp_async16(region + (uint32_t)((hh * BM + r) * KP + c * 16), src, valid);
+        }
+        cp_async_commit();
+    }
+    if (p.talk)
+        for (int i = threadIdx.x; i < HQ * HQ; i += threads) tk[i] = p.talk[i];
+    cp_async_wait<0>();
+    __syncthreads();
+    uint32_t qf[D / 16][4];
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks)
+        ldmatrix_x4(region + (uint32_t)((h * BM + (lane & 15)) * KP + (ks * 2 + (lane >> 4)) * 16), qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
+    __syncthreads();                                          // everybody holds its Q: the region is free for keys
+
+    const uint32_t k_tiles = region, v_tiles = region + (uint32_t)(HKV * BK * KP);
+    const int r0 = lane >> 2, r1 = r0 + 8;
+    const int z0 = z_first + min(r0, n_rows - 1), z1 = z_first + min(r1, n_rows - 1);
+    const int lo0 = first_seen(z0, p.window, p.chunk), lo1 = first_seen(z1, p.window, p.chunk);
+    const int lo_tile = first_seen(z_first, p.window, p.chunk);
+    const float b1 = p.r1 ? p.r1[h] : 0.0f, b2 = p.r2 ? p.r2[h] : 0.0f;
+
+    float o[DV / 8][4];
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+#pragma unroll
+    for (int dt = 0; dt < DV / 8; ++dt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o[dt][i] = 0.0f;
+
+    for (int key0 = lo_tile / BK * BK; key0 <= z_last; key0 += BK) {
+        // the block's keys and values of every kv head
+        {
+            constexpr int KC = D / 8, VC = DV / 8;
+            for (int i = threadIdx.x; i < HKV * BK * (KC + VC); i += threads) {
+                const int c = i % (KC + VC), r = (i / (KC + VC)) % BK, gg = i / ((KC + VC) * BK);
+                const int pos = key0 + r;
+                const bool valid = pos >= lo_tile && pos <= z_last;
+                size_t page_at = 0, slot = 0;
+                if (valid) {
+                    page_at = (size_t)table[pos / p.page_size] * p.page_stride;
+                    slot = (size_t)gg * p.page_size + pos % p.page_size;
+                }
+                if (c < KC) cp_async16(k_tiles + (uint32_t)((gg * BK + r) * KP + c * 16), p.k_base + page_at + slot * D + c * 8, valid);
+                else cp_async16(v_tiles + (uint32_t)((gg * BK + r) * VP + (c - KC) * 16), p.v_base + page_at + slot * DV + (c - KC) * 8, valid);
+            }
+            cp_async_commit();
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        float s[BK / 8][4];
+        warp_qk<D, BK, true>(qf, k_tiles + (uint32_t)(g * BK * KP), 0, s);
+#pragma unroll
+        for (int nt = 0; nt < BK / 8; ++nt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                float v = s[nt][i] * p.scale;
+                if (p.cap > 0.0f) v = p.cap * tanhf(v / p.cap);
+                if (p.r1) {
+                    const int dist = (i < 2 ? z0 : z1) - (key0 + nt * 8 + (lane & 3) * 2 + (i & 1));
+                    v -= b1 * log1pf(b2 * (float)max(dist, 0));
+                }
+                s[nt][i] = v;
+            }
+        if (p.talk) {
+#pragma unroll
+            for (int nt = 0; nt < BK / 8; ++nt) {
+                const int c = nt * 8 + (lane & 3) * 2;
+                *reinterpret_cast<float2*>(sc + ((size_t)h * BM + r0) * SP + c) = make_float2(s[nt][0], s[nt][1]);
+                *reinterpret_cast<float2*>(sc + ((size_t)h * BM + r1) * SP + c) = make_float2(s[nt][2], s[nt][3]);
+            }
+            __syncthreads();
+#pragma unroll
+            for (int nt = 0; nt < BK / 8; ++nt)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) s[nt][i] = 0.0f;
+            for (int j = 0; j < HQ; ++j) {
+                const float w = tk[h * HQ + j];
+#pragma unroll
+                for (int nt = 0; nt < BK / 8; ++nt) {
+                    const int c = nt * 8 + (lane & 3) * 2;
+                    const float2 a = *reinterpret_cast<const float2*>(sc + ((size_t)j * BM + r0) * SP + c);
+                    const float2 b = *reinterpret_cast<const float2*>(sc + ((size_t)j * BM + r1) * SP + c);
+                    s[nt][0] += w * a.x; s[nt][1] += w * a.y; s[nt][2] += w * b.x; s[nt][3] += w * b.y;
+                }
+            }
+        }
+        softmax_update<DV, BK>(s, key0, z0, z1, lo0, lo1, true, LOG2E, m, l, o);
+        warp_pv<DV, BK, true>(s, v_tiles + (uint32_t)(g * BK * VP), 0, o);
+        __syncthreads();                                      // scores and tiles are read before the next block overwrites them
+    }
+    if (p.sink) {
+        const float sk = p.sink[h] * LOG2E;
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const float top = fmaxf(m[k], sk), corr = exp2f(m[k] - top);      // m = -inf cannot happen: a row sees itself
+            l[k] = l[k] * corr + exp2f(sk - top);
+#pragma unroll
+            for (int dt = 0; dt < DV / 8; ++dt) { o[dt][2 * k] *= corr; o[dt][2 * k + 1] *= corr; }
+        }
+    }
+    const float inv0 = l[0] == 0.0f ? 0.0f : 1.0f / l[0], inv1 = l[1] == 0.0f ? 0.0f : 1.0f / l[1];
+    const size_t width = (size_t)HQ * DV;
+#pragma unroll
+    for (int dt = 0; dt < DV / 8; ++dt) {
+        const int d = dt * 8 + (lane & 3) * 2;
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const int r = k ? r1 : r0;
+            if (r >= n_rows) continue;
+            const size_t row = (size_t)(row0 + first + r);
+            float a = o[dt][2 * k] * (k ? inv1 : inv0), b = o[dt][2 * k + 1] * (k ? inv1 : inv0);
+            if (p.gate) {
+                const __nv_bfloat162 gg = *reinterpret_cast<const __nv_bfloat162*>(p.gate + row * p.gate_stride + (size_t)h * DV + d);
+                a *= 1.0f / (1.0f + expf(-__low2float(gg)));
+                b *= 1.0f / (1.0f + expf(-__high2float(gg)));
+            }
+            *(uint32_t*)(p.out + row * width + (size_t)h * DV + d) = pack_bf16(a, b);
+        }
+    }
+}
+
+size_t smem_need(int HQ, int HKV, int D, int DV) {
+    const size_t qb = (size_t)HQ * BM * (D * 2 + 16), kvb = (size_t)HKV * BK * ((D * 2 + 16) + (DV * 2 + 16));
+    const size_t region = ((qb > kvb ? qb : kvb) + 127) / 128 * 128;
+    return region + ((size_t)HQ * BM * SP + (size_t)HQ * HQ) * sizeof(float);
+}
+size_t region_bytes(int HQ, int HKV, int D, int DV) {
+    const size_t qb = (size_t)HQ * BM * (D * 2 + 16), kvb = (size_t)HKV * BK * ((D * 2 + 16) + (DV * 2 + 16));
+    return ((qb > kvb ? qb : kvb) + 127) / 128 * 128;
+}
+bool instantiated(int D, int DV) {
+    return (D == DV && (D == 16 || D == 32 || D == 48 || D == 64 || D == 96 || D == 128)) || (D == 64 && DV == 32) || (D == 32 && DV == 64);
+}
+
+}  // namespace
+
+// 1 when the kernel takes these sizes (head sizes it is built for, a warp per head, everything in shared memory).
+PH_EXPORT int ph_attention_talking_mma_supports(int HQ, int HKV, int D, int DV) {
+    if (HQ < 1 || HKV < 1 || HQ % HKV || HQ > MAX_HEADS || !instantiated(D, DV)) return 0;
+    return smem_need(HQ, HKV, D, DV) <= 227 * 1024 ? 1 : 0;
+}
+
+// q [T, HQ, D], out [T, HQ * DV] and the cache in bfloat16; the gate's rows (null: none) in bfloat16, gate_stride elements
+// apart.  tile_seg / tile_first [n_tiles]: the request and the first row (within its portion) of each tile of 16 rows;
+// every row of the step belongs to one tile.
+PH_EXPORT int ph_attention_talking_mma(const void* q, const void* k_base, const void* v_base, long long page_stride, int page_size,
+                                       const int32_t* block_table, int table_stride, const int32_t* seg_start, const int32_t* seg_ctx_len,
+                                       const int32_t* tile_seg, const int32_t* tile_first, int n_tiles, void* out, int HQ, int HKV, int D,
+                                       int DV, int window, int chunk, float scale, float cap, const float* r1, const float* r2,
+                                       const float* talk, const float* sink, const void* gate, long long gate_stride, cudaStream_t stream) {
+    if (!q || !k_base || !v_base || !block_table || !seg_start || !seg_ctx_len || !tile_seg || !tile_first || !out || n_tiles < 0 ||
+        page_size < 1 || window < 0 || chunk < 0 || (r1 == nullptr) != (r2 == nullptr) || cap < 0.0f)
+        return fail(PH_ERR_ARG, "attention_talking_mma: bad arguments");
+    if (!ph_attention_talking_mma_supports(HQ, HKV, D, DV))
+        return fail(PH_ERR_UNSUPPORTED, "attention_talking_mma: %d / %d heads of %d / %d are not taken", HQ, HKV, D, DV);
+    if ((page_stride * 2) % 16 || ((uintptr_t)k_base | (uintptr_t)v_base | (uintptr_t)q) % 16 || (gate && (gate_stride % 2 || (uintptr_t)gate % 4)))
+        return fail(PH_ERR_ARG, "attention_talking_mma: rows must be 16-byte aligned");
+    if (n_tiles == 0) return PH_OK;
+    TalkParams p;
+    p.q = (const __nv_bfloat16*)q; p.k_base = (const __nv_bfloat16*)k_base; p.v_base = (const __nv_bfloat16*)v_base;
+    p.page_stride = page_stride; p.page_size = page_size; p.block_table = block_table; p.table_stride = table_stride;
+    p.seg_start = seg_start; p.seg_ctx_len = seg_ctx_len; p.tile_seg = tile_seg; p.tile_first = tile_first;
+    p.out = (__nv_bfloat16*)out; p.HQ = HQ; p.HKV = HKV; p.window = window; p.chunk = chunk; p.scale = scale; p.cap = cap;
+    p.r1 = r1; p.r2 = r2; p.talk = talk; p.sink = sink; p.gate = (const __nv_bfloat16*)gate; p.gate_stride = gate_stride;
+    p.kv_bytes = (int)region_bytes(HQ, HKV, D, DV);
+    const size_t smem = smem_need(HQ, HKV, D, DV);
+#define CASE(DD, VV)                                                                                                      \
+    if (D == DD && DV == VV) {                                                                                            \
+        auto kern = attention_talking_mma_kernel<DD, VV>;                                                                 \
+        if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
+            return fail(PH_ERR_LAUNCH, "attention_talking_mma: %zu bytes of shared memory were refused", smem);           \
+        kern<<<n_tiles, HQ * 32, smem, stream>>>(p);                                                                      \
+        return check_launch("attention_talking_mma");                                                                     \
+    }
+    CASE(16, 16) CASE(32, 32) CASE(48, 48) CASE(64, 64) CASE(96, 96) CASE(128, 128) CASE(64, 32) CASE(32, 64)
+#undef CASE
+    return fail(PH_ERR_UNSUPPORTED, "attention_talking_mma: head sizes %d / %d", D, DV);
+}

@@ -30,8 +30,8 @@ LIBRARIES: Dict[str, dict] = {
     "core": {
         "sources": ["elementwise.cu", "qk_norm_rope.cu", "attention_generic.cu", "gemm_simple.cu", "sampling.cu",
                     "random_fill.cu", "layernorm.cu", "gated.cu", "mamba.cu", "moe.cu", "linear_attention.cu", "dyntanh.cu",
-                    "latent_attention.cu", "attention_talking.cu", "min_gru.cu", "core_lib.cu"],
-        "deps": ["../weights/random.h"],
+                    "latent_attention.cu", "attention_talking.cu", "attention_talking_mma.cu", "min_gru.cu", "core_lib.cu"],
+        "deps": ["../weights/random.h", "attention_mma.cuh"],
         "flags": [],
         "link": [],
     },

@@ -180,6 +180,8 @@ const CoreKernels& core_kernels() {
     bind(h, "core", "ph_latent_expand", g_core.latent_expand);
     bind(h, "core", "ph_attention_generic_sink", g_core.attention_generic_sink);
     bind(h, "core", "ph_attention_talking", g_core.attention_talking);
+    bind(h, "core", "ph_attention_talking_mma", g_core.attention_talking_mma);
+    bind(h, "core", "ph_attention_talking_mma_supports", g_core.attention_talking_mma_supports);
     bind(h, "core", "ph_joint_norm_kv_write", g_core.joint_norm_kv_write);
     bind(h, "core", "ph_min_gru_scan", g_core.min_gru_scan);
     bind(h, "core", "ph_pair_sum", g_core.pair_sum);

@@ -163,6 +163,11 @@ struct CoreKernels {
     int (*attention_talking)(const void*, int, const void*, const void*, int, long long, int, const int32_t*, int, const int32_t*,
                              const int32_t*, void*, int, int, int, int, int, int, int, int, float, float, const float*, const float*,
                              const float*, const float*, const void*, int, long long, cudaStream_t);
+    // the same attention on the tensor cores (bfloat16), a tile of 16 rows and all heads per CTA
+    int (*attention_talking_mma)(const void*, const void*, const void*, long long, int, const int32_t*, int, const int32_t*, const int32_t*,
+                                 const int32_t*, const int32_t*, int, void*, int, int, int, int, int, int, float, float, const float*,
+                                 const float*, const float*, const float*, const void*, long long, cudaStream_t);
+    int (*attention_talking_mma_supports)(int, int, int, int);
     int (*joint_norm_kv_write)(const void*, int, int, long long, long long, const float*, const float*, float, const int32_t*, void*, int,
                                void*, void*, int, long long, int, int, int, int, int, int, int, cudaStream_t);
     // a minimal gated recurrent unit over the rows of each request; the weighted sum of two mixers' outputs

@@ -35,6 +35,7 @@ namespace {
 constexpr int kBlockKeys = 64, kMaxSplits = 32;
 constexpr int kTile = 64;          // rows of a query tile of the mma.sync prefill kernel
 constexpr int kTileLarge = 128;    // rows of a query tile of the tcgen05 prefill kernel
+constexpr int kTileAll = 16;       // rows of a tile of the kernel that takes all heads of a tile at once
 constexpr int kCtasPerSm = 3;      // cp.async decode CTAs that fit one SM (68 KB of shared memory each at head_dim 128)
 inline int ceil_div(long long a, long long b) { return (int)((a + b - 1) / b); }
 
@@ -91,15 +92,15 @@ int tc5_splits(int n_tiles, int heads, int max_ctx, int sms, int window) {
 }
 
 // The prompt portions of a step cut into tiles of `rows` rows: segment and first row (within the portion) of
-// each tile.  The tiles that look furthest back come first: the grid starts them first and the short ones fill
-// the tail.
-void add_tiles(StepPlan& plan, int rows, const std::string& name) {
+// each tile (single_rows: a decode row is a tile too, so that every row of the step is in one).  The tiles that look
+// furthest back come first: the grid starts them first and the short ones fill the tail.
+void add_tiles(StepPlan& plan, int rows, const std::string& name, bool single_rows = false) {
     if (plan.has(name + ".seg")) return;
     struct Tile { int seg, first, reach; };
     std::vector<Tile> tiles;
     for (int s = 0; s < plan.S; s++) {
         const int n = plan.q_lens[s];
-        if (n == 1) continue;
+        if (n == 1 && !single_rows) continue;
         for (int first = 0; first < n; first += rows)
             tiles.push_back({s, first, plan.ctx_lens[s] - n + std::min(first + rows, n)});
     }
@@ -248,7 +249,14 @@ public:
     // ---- cache and step metadata ------------------------------------------------------------------------------
     CacheNeed cache_need() const override { return CacheNeed::pages(kv_heads_, head_dim_, window_, value_dim_, chunk_); }
 
+    // attention with a sink in bfloat16 runs on the tensor-core kernel that knows sinks (a tile of 16 rows, all heads)
+    bool use_sink_kernel() const {
+        return has_sink_ && compute_dtype == DType::BF16 && attention_ != "generic" && !chunk_ &&
+               core_kernels().attention_talking_mma_supports(heads_, kv_heads_, head_dim_, value_dim_);
+    }
+
     void prepare_step(StepPlan& plan) override {
+        if (use_sink_kernel()) add_tiles(plan, kTileAll, "attention.tiles16", true);
         if (!use_flash()) return;
         bool portions = false;
         for (int n : plan.q_lens) portions |= n > 1;
@@ -318,9 +326,15 @@ public:
             LaunchProfile::get().note_cost(read * kv_heads_ * (head_dim_ + value_dim_) * kv + (double)T * (q_width_ + o_width_) * dtype_size(dt),
                                            2.0 * seen * heads_ * (head_dim_ + value_dim_));
         }
+        const StepArray t16 = ctx.array("attention.tiles16.seg"), t16f = ctx.array("attention.tiles16.first");
         if (use_flash()) {
             if (cache.kv_dtype != DType::BF16) throw KernelError("attention_flash: the cache must be bfloat16");
             flash(q, cache, g, ctx, out, abs_positions);
+        } else if (use_sink_kernel() && cache.kv_dtype == DType::BF16 && t16.count) {
+            QE_LAUNCH(core, core.attention_talking_mma(q.data, cache.k_base, cache.v_base, cache.page_stride, cache.page_size, g.block_table,
+                                                       g.table_width, ctx.seg_start, ctx.seg_ctx_len, t16.data, t16f.data, t16.count, out.data,
+                                                       heads_, kv_heads_, head_dim_, value_dim_, window_, 0, (float)scale_, 0.0f, nullptr,
+                                                       nullptr, nullptr, sink_.as<float>(), nullptr, 0, ctx.stream));
         } else {
             QE_LAUNCH(core, core.attention_generic_sink(q.data, q.code(), cache.k_base, cache.v_base, (int)cache.kv_dtype, cache.page_stride,
                                                         cache.page_size, g.block_table, g.table_width, ctx.row_seg, abs_positions, out.data,
@@ -437,6 +451,7 @@ public:
         has_sink_ = names_.count("sink") != 0;
         has_gate_ = names_.count("gate_proj") != 0;
         gemm_ = b.options.get_string("gemm", "auto");
+        attention_ = b.options.get_string("attention", "auto");
         q_width_ = (int64_t)heads_ * head_dim_;
         kv_width_ = (int64_t)kv_heads_ * head_dim_;
         v_width_ = values_are_keys_ ? 0 : (int64_t)kv_heads_ * value_dim_;
@@ -498,6 +513,15 @@ public:
     int preferred_row_multiple() const override { return (in_proj_.fast() || o_proj_.fast()) ? 256 : 0; }
     CacheNeed cache_need() const override { return CacheNeed::pages(kv_heads_, head_dim_, window_, value_dim_); }
 
+    // bfloat16 with sizes the tensor-core kernel takes: a tile of 16 rows and all heads per CTA; else the plain kernel
+    bool use_mma() const {
+        return compute_dtype == DType::BF16 && attention_ != "generic" &&
+               core_kernels().attention_talking_mma_supports(heads_, kv_heads_, head_dim_, value_dim_);
+    }
+    void prepare_step(StepPlan& plan) override {
+        if (use_mma()) add_tiles(plan, kTileAll, "attention.tiles16", true);
+    }
+
     Addend forward(const Tensor& x, StepContext& ctx, const CacheView& cache) override {
         if (!cache.writable) throw Error(kInvalidState, "talking_attention writes a cache of its own");
         const int T = ctx.T;
@@ -536,12 +560,21 @@ public:
                                                (double)T * (q_width_ + o_width_ + g_width_) * dtype_size(dt),
                                            2.0 * seen * heads_ * (head_dim_ + value_dim_ + (has_mix_ ? heads_ : 0)));
         }
-        QE_LAUNCH(core, core.attention_talking(q.data, q.code(), cache.k_base, cache.v_base, (int)cache.kv_dtype, cache.page_stride, cache.page_size,
-                                               g.block_table, g.table_width, ctx.row_seg, ctx.position_column(0), out.data, out.code(), T, heads_,
-                                               kv_heads_, head_dim_, value_dim_, window_, 0, (float)scale_, (float)softcap_,
-                                               has_distance_ ? slope_.as<float>() : nullptr, has_distance_ ? rate_.as<float>() : nullptr,
-                                               has_mix_ ? mix_.as<float>() : nullptr, has_sink_ ? sink_.as<float>() : nullptr, gate, gate_code,
-                                               gate_stride, ctx.stream));
+        const StepArray t16 = ctx.array("attention.tiles16.seg"), t16f = ctx.array("attention.tiles16.first");
+        if (use_mma() && cache.kv_dtype == DType::BF16 && t16.count && (!gate || in.tensor.dtype == DType::BF16))
+            QE_LAUNCH(core, core.attention_talking_mma(q.data, cache.k_base, cache.v_base, cache.page_stride, cache.page_size, g.block_table,
+                                                       g.table_width, ctx.seg_start, ctx.seg_ctx_len, t16.data, t16f.data, t16.count, out.data,
+                                                       heads_, kv_heads_, head_dim_, value_dim_, window_, 0, (float)scale_, (float)softcap_,
+                                                       has_distance_ ? slope_.as<float>() : nullptr, has_distance_ ? rate_.as<float>() : nullptr,
+                                                       has_mix_ ? mix_.as<float>() : nullptr, has_sink_ ? sink_.as<float>() : nullptr, gate,
+                                                       gate_stride, ctx.stream));
+        else
+            QE_LAUNCH(core, core.attention_talking(q.data, q.code(), cache.k_base, cache.v_base, (int)cache.kv_dtype, cache.page_stride, cache.page_size,
+                                                   g.block_table, g.table_width, ctx.row_seg, ctx.position_column(0), out.data, out.code(), T, heads_,
+                                                   kv_heads_, head_dim_, value_dim_, window_, 0, (float)scale_, (float)softcap_,
+                                                   has_distance_ ? slope_.as<float>() : nullptr, has_distance_ ? rate_.as<float>() : nullptr,
+                                                   has_mix_ ? mix_.as<float>() : nullptr, has_sink_ ? sink_.as<float>() : nullptr, gate, gate_code,
+                                                   gate_stride, ctx.stream));
         return o_proj_(out, ctx, "talk_o", DType::F32, T, true, false, ctx.residual, nullptr, &ctx.norm_ahead);
     }
 
@@ -550,7 +583,7 @@ private:
     int heads_, kv_heads_, head_dim_, value_dim_, window_;
     bool values_are_keys_, has_norm_, has_distance_, has_mix_, has_sink_, has_gate_;
     double eps_, scale_, softcap_;
-    std::string gemm_;
+    std::string gemm_, attention_;
     Linear in_proj_, o_proj_;
     Tensor q_norm_, k_norm_, slope_, rate_, mix_, sink_;
 };

@@ -231,13 +231,17 @@ def sharp_model(tmp, kind_m, width, seed, storage):
     return cfg, w, make_folder(tmp, cfg, w, storage)
 
 
-# windows of 70, 33, 200 and 9 positions and none; groups of 1, 2, 3 and 4; one head alone (nobody to talk to) and twelve
+# windows of 9 to 200 positions and none; groups of 1 to 5; one head alone (nobody to talk to) and sixteen; heads of 16, 32,
+# 48, 64 and 96 take the tensor-core kernel in bfloat16, the others the plain one
 TALKERS = {
     "h4": (talking(4, 2, 16, 70, scale=2.0, softcap=8.0), 64),
     "h6": (talking(6, 2, 24, 33, scale=1.5, softcap=30.0), 48),
     "h12": (talking(12, 3, 8, 200, scale=3.0), 64),
     "h1": (talking(1, 1, 40, None, scale=1.0, softcap=2.0), 40),
     "h3": (talking(3, 3, 64, 9, scale=0.8, softcap=6.0), 24),
+    "h5": (talking(5, 1, 32, 100, scale=1.2, softcap=10.0), 56),
+    "h8": (talking(8, 2, 48, 45, scale=1.0), 72),
+    "h16": (talking(16, 4, 96, 130, scale=0.7, softcap=12.0), 64),
 }
 
 
@@ -281,12 +285,14 @@ def test_talking_attention_alone_whole_cut_decoded_and_batched(tmp_path, which, 
     close(np.concatenate([both[1:], again[:2]]), ref[:92], tol)
 
 
-# the left side alone: heads of 64 and 128 (the sizes the tensor-core kernels take) and others; values narrower and wider
+# the left side alone: heads of 48, 64 and 128 (sizes the tensor-core kernel takes) and others; values narrower and wider
 LEFTS = {
     "d64": (left_side(4, 2, 64, 64, 70, 32, base=300.0, scale=0.6), 64),
     "d128": (left_side(2, 1, 128, 128, 33, 128, base=1e4, scale=0.4), 48),
     "d24": (left_side(3, 3, 24, 40, 50, 2, base=5e5, scale=1.0), 64),
     "d16": (left_side(8, 2, 16, 8, None, 0, scale=1.2), 40),
+    "d64v": (left_side(4, 4, 64, 32, 100, 16, base=77.0, scale=0.5), 40),
+    "d48": (left_side(6, 2, 48, 48, 17, 48, base=1e3, scale=0.7), 72),
 }
 
 
@@ -444,12 +450,14 @@ def test_the_head_scales_and_caps_the_logits(models):
     from purhie_b200.parts import PartProbe
     for name in ("A", "B", "C"):
         folder, cfg, w = models[name]
-        xn = np.random.default_rng(0).normal(0, 4.0, (5, cfg["width"])).astype(np.float32)
+        xn = np.random.default_rng(0).normal(0, 12.0, (5, cfg["width"])).astype(np.float32)
         y = xn.astype(np.float64) @ w["embed"].T * cfg.get("logit_scale", 1.0)
         ref = P.soft_cap(y, cfg["logit_softcap"]) if cfg.get("logit_softcap") else y
         if cfg.get("logit_softcap"):
             assert np.abs(y).max() > 1.2 * np.abs(ref).max()                 # the cap bites
-        p = PartProbe("head", *part_of(cfg, None, "head"))
+        kind, params = part_of(cfg, None, "head")
+        params = {k: v for k, v in params.items() if k != "tied_to"}          # alone, the head reads the table under its own name
+        p = PartProbe("head", kind, dict(params, names={"weight": "embed"}))
         p.bind_folder(folder)
         close(p.head(xn, cfg["vocab"]), ref, 2e-4)
 
