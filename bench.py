@@ -2,7 +2,7 @@
 """Decode and prefill throughput of the engine at the Qwen3-8B shape with random weights, on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--shape 8b|0.6b|32b] [--impl ours|reference]
-    python bench.py --design bozosun|sizizen|zerusun [--size 2k|4k]   (another design beside the Qwen3 layers of equal size; see below)
+    python bench.py --design bozosun|sizizen|zerusun|vokepel [--size 1k|2k|4k]   (another design beside the Qwen3 layers of equal size; see below)
 
 Prints ONE JSON line.  ``value`` is decoded tokens per second at batch 8 from 2,048-token prefixes, timed on the
 device (CUDA events on the engine's stream) over exactly K decode steps after W warm-up steps, each step fed its
@@ -99,6 +99,8 @@ class ClockSampler:
 # Layer sizes that resemble a real model's, random weights.  Four layers, one of every pairing of the design's mixers
 # and feed-forwards; the twin is four Qwen3 layers of the same width, heads and feed-forward width.
 DESIGN_SIZES = {
+    "1k": dict(width=1024, heads=8, kv_heads=2, dim=128, ff=4096, inner=2048, state=16, dt_rank=64, conv=4, experts=8, top=2,
+               expert_ff=2048, vocab=32768),
     "2k": dict(width=2048, heads=16, kv_heads=4, dim=128, ff=8192, inner=4096, state=16, dt_rank=128, conv=4, experts=8, top=2,
                expert_ff=4096, vocab=32768),
     "4k": dict(width=4096, heads=32, kv_heads=8, dim=128, ff=12288, inner=8192, state=16, dt_rank=256, conv=4, experts=16, top=4,
@@ -152,7 +154,26 @@ def zerusun_config(z):
             "loop": {"start": 1, "stop": 3, "times": 1}, "max_position": CONTEXT}
 
 
-DESIGN_CONFIGS = {"bozosun": bozosun_config, "sizizen": sizizen_config, "zerusun": zerusun_config}
+def vokepel_config(z):
+    """Four pre-norm layers with a factor on the residual and squared-relu feed-forwards: attention whose heads talk before
+    the softmax (capped scores, a distance bias, a window of 1,024 positions, keys that double as values, a sigmoid gate)
+    in the first and third, attention with a sink (heads of 128 rotated over their whole width in interleaved pairs, the
+    same window) side by side with a minimal gated recurrent unit as wide as the model in the second and fourth.  The two
+    middle layers are the repeated stretch, run once, so that the reinjection in front of it is in the step and the
+    number of layer runs equals the twin's."""
+    att = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"], "mask": {"size": 1024},
+           "scale": z["dim"] ** -0.5, "softcap": 30.0}
+    left = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"], "mask": {"size": 1024},
+            "rot": {"base": 5e5, "dims": z["dim"]}, "scale": z["dim"] ** -0.5}
+    both = {"left": left, "right": {"width": z["width"]}, "left_scale": 0.6, "right_scale": 1.1}
+    dense = {"kind": "dense", "ff": z["ff"]}
+    layers = [{"type": "attention", "mixer": att, "mlp": dense}, {"type": "parallel", "mixer": both, "mlp": dense},
+              {"type": "attention", "mixer": att, "mlp": dense}, {"type": "parallel", "mixer": both, "mlp": dense}]
+    return {"architecture": "Vokepel", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6}, "residual_mult": 0.7,
+            "logit_scale": 2.0, "logit_softcap": 30.0, "layers": layers, "loop": {"start": 1, "stop": 3, "times": 1}, "max_position": CONTEXT}
+
+
+DESIGN_CONFIGS = {"bozosun": bozosun_config, "sizizen": sizizen_config, "zerusun": zerusun_config, "vokepel": vokepel_config}
 
 
 def design_bench(args):
@@ -242,7 +263,7 @@ def main():
     ap.add_argument("--page-size", type=int, default=16, help="tokens per cache page (the benchmark's configuration has 16)")
     ap.add_argument("--step-options", default="", metavar="JSON",
                     help="kernel choices of the step, for comparing two forms of it on one box, e.g. '{\"norm_ahead\": \"off\"}'")
-    ap.add_argument("--design", default="", choices=["", "bozosun", "sizizen", "zerusun"],
+    ap.add_argument("--design", default="", choices=["", "bozosun", "sizizen", "zerusun", "vokepel"],
                     help="instead of the headline workload: prefill and decode of this design at real layer sizes beside four "
                          "Qwen3 layers of equal size, with the time and roofline fraction of every kernel class")
     ap.add_argument("--size", default="4k", choices=sorted(DESIGN_SIZES), help="with --design: the layer sizes")

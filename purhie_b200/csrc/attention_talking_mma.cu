@@ -35,7 +35,18 @@ struct TalkParams {
     const float* r1; const float* r2; const float* talk; const float* sink;
     const __nv_bfloat16* gate; long long gate_stride;
     int kv_bytes;                 // bytes of the region that holds Q first and the blocks of K and V afterwards
+    int splits;                   // CTAs that share a tile's keys (blockIdx.y); above 1 they leave partial results
+    float* part_o;                // [T][HQ][splits][DV] float32, unnormalised
+    float* part_ml;               // [T][HQ][splits][2]: the exponent's reference (log2 domain) and the sum
 };
+
+// tanh and ln(1 + x) from the hardware's exponential and logarithm: a few float32 operations each with errors near 1e-6,
+// far below what the bfloat16 weights of the softmax keep
+__device__ __forceinline__ float fast_tanh(float x) {
+    const float e = __expf(-2.0f * fabsf(x));
+    return copysignf(__fdividef(1.0f - e, 1.0f + e), x);
+}
+__device__ __forceinline__ float fast_log1p(float x) { return x < 0.25f ? log1pf(x) : __logf(1.0f + x); }
 
 template <int D, int DV>
 __global__ void __launch_bounds__(MAX_HEADS * 32) attention_talking_mma_kernel(const TalkParams p) {
@@ -91,7 +102,15 @@ __global__ void __launch_bounds__(MAX_HEADS * 32) attention_talking_mma_kernel(c
 #pragma unroll
         for (int i = 0; i < 4; ++i) o[dt][i] = 0.0f;
 
-    for (int key0 = lo_tile / BK * BK; key0 <= z_last; key0 += BK) {
+    // this CTA's share of the tile's key blocks
+    int kb_first = lo_tile / BK, kb_last = z_last / BK;
+    if (p.splits > 1) {
+        const int per = (kb_last - kb_first + p.splits) / p.splits;
+        kb_first += (int)blockIdx.y * per;
+        kb_last = min(kb_last, kb_first + per - 1);
+    }
+    const bool upper = n_rows > 8;                            // rows 8 .. 15 of the tile exist
+    for (int key0 = kb_first * BK; key0 <= kb_last * BK; key0 += BK) {
         // the block's keys and values of every kv head
         {
             constexpr int KC = D / 8, VC = DV / 8;
@@ -117,11 +136,12 @@ __global__ void __launch_bounds__(MAX_HEADS * 32) attention_talking_mma_kernel(c
         for (int nt = 0; nt < BK / 8; ++nt)
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
+                if (i >= 2 && !upper) continue;              // a tile of few rows (a decode row) skips the copies of its last row
                 float v = s[nt][i] * p.scale;
-                if (p.cap > 0.0f) v = p.cap * tanhf(v / p.cap);
+                if (p.cap > 0.0f) v = p.cap * fast_tanh(__fdividef(v, p.cap));
                 if (p.r1) {
                     const int dist = (i < 2 ? z0 : z1) - (key0 + nt * 8 + (lane & 3) * 2 + (i & 1));
-                    v -= b1 * log1pf(b2 * (float)max(dist, 0));
+                    v -= b1 * fast_log1p(b2 * (float)max(dist, 0));
                 }
                 s[nt][i] = v;
             }
@@ -143,14 +163,34 @@ __global__ void __launch_bounds__(MAX_HEADS * 32) attention_talking_mma_kernel(c
                 for (int nt = 0; nt < BK / 8; ++nt) {
                     const int c = nt * 8 + (lane & 3) * 2;
                     const float2 a = *reinterpret_cast<const float2*>(sc + ((size_t)j * BM + r0) * SP + c);
-                    const float2 b = *reinterpret_cast<const float2*>(sc + ((size_t)j * BM + r1) * SP + c);
-                    s[nt][0] += w * a.x; s[nt][1] += w * a.y; s[nt][2] += w * b.x; s[nt][3] += w * b.y;
+                    s[nt][0] += w * a.x; s[nt][1] += w * a.y;
+                    if (upper) {
+                        const float2 b = *reinterpret_cast<const float2*>(sc + ((size_t)j * BM + r1) * SP + c);
+                        s[nt][2] += w * b.x; s[nt][3] += w * b.y;
+                    }
                 }
             }
         }
         softmax_update<DV, BK>(s, key0, z0, z1, lo0, lo1, true, LOG2E, m, l, o);
         warp_pv<DV, BK, true>(s, v_tiles + (uint32_t)(g * BK * VP), 0, o);
         __syncthreads();                                      // scores and tiles are read before the next block overwrites them
+    }
+    if (p.splits > 1) {
+        // (reference, sum, unnormalised output) of this CTA's keys; the merge adds the sink and the gate
+        const int T_HQ = HQ;
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const int r = k ? r1 : r0;
+            if (r >= n_rows) continue;
+            const size_t slot = ((size_t)(row0 + first + r) * T_HQ + h) * p.splits + blockIdx.y;
+            if ((lane & 3) == 0) { p.part_ml[slot * 2] = m[k]; p.part_ml[slot * 2 + 1] = l[k]; }
+#pragma unroll
+            for (int dt = 0; dt < DV / 8; ++dt) {
+                const int d = dt * 8 + (lane & 3) * 2;
+                *reinterpret_cast<float2*>(p.part_o + slot * DV + d) = make_float2(o[dt][2 * k], o[dt][2 * k + 1]);
+            }
+        }
+        return;
     }
     if (p.sink) {
         const float sk = p.sink[h] * LOG2E;
@@ -183,6 +223,32 @@ __global__ void __launch_bounds__(MAX_HEADS * 32) attention_talking_mma_kernel(c
     }
 }
 
+// One block per (row, head): the partial results of the key splits merged in ascending order, then the sink and the gate.
+__global__ void attention_talking_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, int splits,
+                                               const float* __restrict__ sink, const __nv_bfloat16* __restrict__ gate, long long gate_stride,
+                                               __nv_bfloat16* __restrict__ out, int HQ, int DV) {
+    const int t = blockIdx.x, h = blockIdx.y;
+    const size_t slot0 = ((size_t)t * HQ + h) * splits;
+    float top = sink ? sink[h] * LOG2E : -INFINITY;
+    for (int s = 0; s < splits; ++s) top = fmaxf(top, part_ml[(slot0 + s) * 2]);
+    float l = sink ? exp2f(sink[h] * LOG2E - top) : 0.0f;
+    for (int s = 0; s < splits; ++s) {
+        const float ms = part_ml[(slot0 + s) * 2];
+        if (ms != -INFINITY) l += exp2f(ms - top) * part_ml[(slot0 + s) * 2 + 1];
+    }
+    const float inv = l == 0.0f ? 0.0f : 1.0f / l;
+    for (int d = threadIdx.x; d < DV; d += blockDim.x) {
+        float acc = 0.0f;
+        for (int s = 0; s < splits; ++s) {
+            const float ms = part_ml[(slot0 + s) * 2];
+            if (ms != -INFINITY) acc += exp2f(ms - top) * part_o[(slot0 + s) * DV + d];
+        }
+        float v = acc * inv;
+        if (gate) v *= 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)t * gate_stride + (size_t)h * DV + d])));
+        out[((size_t)t * HQ + h) * DV + d] = __float2bfloat16_rn(v);
+    }
+}
+
 size_t smem_need(int HQ, int HKV, int D, int DV) {
     const size_t qb = (size_t)HQ * BM * (D * 2 + 16), kvb = (size_t)HKV * BK * ((D * 2 + 16) + (DV * 2 + 16));
     const size_t region = ((qb > kvb ? qb : kvb) + 127) / 128 * 128;
@@ -206,14 +272,17 @@ PH_EXPORT int ph_attention_talking_mma_supports(int HQ, int HKV, int D, int DV) 
 
 // q [T, HQ, D], out [T, HQ * DV] and the cache in bfloat16; the gate's rows (null: none) in bfloat16, gate_stride elements
 // apart.  tile_seg / tile_first [n_tiles]: the request and the first row (within its portion) of each tile of 16 rows;
-// every row of the step belongs to one tile.
+// every row of the step belongs to one tile.  splits > 1: that many CTAs share each tile's keys and leave partial results
+// in part_o [T][HQ][splits][DV] and part_ml [T][HQ][splits][2] (float32), which a second kernel merges over all T rows.
 PH_EXPORT int ph_attention_talking_mma(const void* q, const void* k_base, const void* v_base, long long page_stride, int page_size,
                                        const int32_t* block_table, int table_stride, const int32_t* seg_start, const int32_t* seg_ctx_len,
                                        const int32_t* tile_seg, const int32_t* tile_first, int n_tiles, void* out, int HQ, int HKV, int D,
                                        int DV, int window, int chunk, float scale, float cap, const float* r1, const float* r2,
-                                       const float* talk, const float* sink, const void* gate, long long gate_stride, cudaStream_t stream) {
+                                       const float* talk, const float* sink, const void* gate, long long gate_stride, int splits, int T,
+                                       float* part_o, float* part_ml, cudaStream_t stream) {
     if (!q || !k_base || !v_base || !block_table || !seg_start || !seg_ctx_len || !tile_seg || !tile_first || !out || n_tiles < 0 ||
-        page_size < 1 || window < 0 || chunk < 0 || (r1 == nullptr) != (r2 == nullptr) || cap < 0.0f)
+        page_size < 1 || window < 0 || chunk < 0 || (r1 == nullptr) != (r2 == nullptr) || cap < 0.0f || splits < 1 || splits > 64 ||
+        (splits > 1 && (!part_o || !part_ml || T < 1 || ((uintptr_t)part_o % 8))))
         return fail(PH_ERR_ARG, "attention_talking_mma: bad arguments");
     if (!ph_attention_talking_mma_supports(HQ, HKV, D, DV))
         return fail(PH_ERR_UNSUPPORTED, "attention_talking_mma: %d / %d heads of %d / %d are not taken", HQ, HKV, D, DV);
@@ -227,13 +296,17 @@ PH_EXPORT int ph_attention_talking_mma(const void* q, const void* k_base, const 
     p.out = (__nv_bfloat16*)out; p.HQ = HQ; p.HKV = HKV; p.window = window; p.chunk = chunk; p.scale = scale; p.cap = cap;
     p.r1 = r1; p.r2 = r2; p.talk = talk; p.sink = sink; p.gate = (const __nv_bfloat16*)gate; p.gate_stride = gate_stride;
     p.kv_bytes = (int)region_bytes(HQ, HKV, D, DV);
+    p.splits = splits; p.part_o = part_o; p.part_ml = part_ml;
     const size_t smem = smem_need(HQ, HKV, D, DV);
 #define CASE(DD, VV)                                                                                                      \
     if (D == DD && DV == VV) {                                                                                            \
         auto kern = attention_talking_mma_kernel<DD, VV>;                                                                 \
         if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
             return fail(PH_ERR_LAUNCH, "attention_talking_mma: %zu bytes of shared memory were refused", smem);           \
-        kern<<<n_tiles, HQ * 32, smem, stream>>>(p);                                                                      \
+        kern<<<dim3(n_tiles, splits), HQ * 32, smem, stream>>>(p);                                                        \
+        if (splits > 1)                                                                                                   \
+            attention_talking_merge_kernel<<<dim3(T, HQ), DV >= 64 ? 64 : 32, 0, stream>>>(part_o, part_ml, splits, sink, p.gate, gate_stride, \
+                                                                                             p.out, HQ, DV);               \
         return check_launch("attention_talking_mma");                                                                     \
     }
     CASE(16, 16) CASE(32, 32) CASE(48, 48) CASE(64, 64) CASE(96, 96) CASE(128, 128) CASE(64, 32) CASE(32, 64)

@@ -31,7 +31,7 @@ __global__ void embed_gather_kernel(const TT* __restrict__ table, const int32_t*
 template <typename TA, typename TY, int NT>
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TA* __restrict__ add, int add_splits,
                                    long long add_split_stride, const float* __restrict__ weight, float eps,
-                                   const int32_t* __restrict__ rows, int E, TY* __restrict__ y, int write_x) {
+                                   const int32_t* __restrict__ rows, int E, TY* __restrict__ y, int write_x, float add_scale) {
     extern __shared__ float row_buf[];
     __shared__ float scratch[32];
     const int r = blockIdx.x;
@@ -42,7 +42,13 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TA* __restrict__
         float v = xr[i];
         if (add) {
             const TA* a = add + (size_t)t * E + i;
-            for (int s = 0; s < add_splits; ++s) v += to_float<TA>(a[(size_t)s * add_split_stride]);
+            if (add_scale == 1.0f) {
+                for (int s = 0; s < add_splits; ++s) v += to_float<TA>(a[(size_t)s * add_split_stride]);
+            } else {                      // the addend as a whole times its factor
+                float u = 0.0f;
+                for (int s = 0; s < add_splits; ++s) u += to_float<TA>(a[(size_t)s * add_split_stride]);
+                v += add_scale * u;
+            }
             if (write_x) xr[i] = v;
         }
         row_buf[i] = v;
@@ -87,7 +93,7 @@ constexpr int MANY_PARTS_IN_FLIGHT = 12;
 template <typename TA, typename TY, int MAX_IT, int PARTS_IN_FLIGHT>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const TA* __restrict__ add, int add_splits,
                                        long long add_split_stride, const float* __restrict__ weight, float eps,
-                                       const int32_t* __restrict__ rows, int E, TY* __restrict__ y, int write_x) {
+                                       const int32_t* __restrict__ rows, int E, TY* __restrict__ y, int write_x, float add_scale) {
     __shared__ float scratch[128];
     pdl_launch_dependents();
     // what no kernel of this step writes (the norm's weight, the row list) is fetched while the kernel in front
@@ -112,6 +118,8 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const TA* __restri
             float4 acc = Vec4<float>::load(xr + i);
             if (add) {
                 const TA* a = add + (size_t)t * E + i;
+                const float4 base = acc;
+                if (add_scale != 1.0f) acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);   // the addend is summed alone, then scaled
                 for (int s0 = 0; s0 < add_splits; s0 += PARTS_IN_FLIGHT) {      // loads in flight, added in order
                     float4 u[PARTS_IN_FLIGHT];
 #pragma unroll
@@ -122,6 +130,8 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const TA* __restri
                     for (int j = 0; j < PARTS_IN_FLIGHT; ++j)
                         if (s0 + j < add_splits) { acc.x += u[j].x; acc.y += u[j].y; acc.z += u[j].z; acc.w += u[j].w; }
                 }
+                if (add_scale != 1.0f)
+                    acc = make_float4(base.x + add_scale * acc.x, base.y + add_scale * acc.y, base.z + add_scale * acc.z, base.w + add_scale * acc.w);
                 if (write_x) Vec4<float>::store(xr + i, acc);
             }
             v[it] = acc;
@@ -274,9 +284,10 @@ PH_EXPORT int ph_embed_gather(const void* table, int table_dtype, const int32_t*
     return check_launch("embed_gather");
 }
 
-PH_EXPORT int ph_add_rmsnorm(float* x, const void* add, int add_dtype, int add_splits, long long add_split_stride,
+// As add_rmsnorm with a factor on the addend: v = x + add_scale * (sum of the addend's parts).
+PH_EXPORT int ph_add_scaled_rmsnorm(float* x, const void* add, int add_dtype, int add_splits, long long add_split_stride,
                              const float* weight, float eps, const int32_t* rows, int n_out, int E, void* y,
-                             int y_dtype, int write_x, cudaStream_t stream) {
+                             int y_dtype, int write_x, float add_scale, cudaStream_t stream) {
     if (!x || n_out < 0 || E < 1 || !valid_dtype(add_dtype) || !valid_dtype(y_dtype) || (weight && !y) ||
         (add && add_splits < 1))
         return fail(PH_ERR_ARG, "add_rmsnorm: bad arguments (rows %d, E %d)", n_out, E);
@@ -296,11 +307,11 @@ PH_EXPORT int ph_add_rmsnorm(float* x, const void* add, int add_dtype, int add_s
         do {                                                                                                            \
             if (!add || add_splits == 1)                                                                                \
                 launch_overlapped(add_rmsnorm_vec_kernel<TA, TY, IT, 1>, dim3(n_out), dim3(threads), 0, stream, x,      \
-                                  (const TA*)add, add_splits, add_split_stride, weight, eps, rows, E, (TY*)y, write_x); \
+                                  (const TA*)add, add_splits, add_split_stride, weight, eps, rows, E, (TY*)y, write_x, add_scale); \
             else                                                                                                        \
                 launch_overlapped(add_rmsnorm_vec_kernel<TA, TY, IT, MANY_PARTS_IN_FLIGHT>, dim3(n_out), dim3(threads), \
                                   0, stream, x, (const TA*)add, add_splits, add_split_stride, weight, eps, rows, E,     \
-                                  (TY*)y, write_x);                                                                     \
+                                  (TY*)y, write_x, add_scale);                                                          \
         } while (0)
         PH_DISPATCH(add_dtype, TA, PH_DISPATCH(y_dtype, TY, {
             if (iters == 1) LAUNCH_VEC(TA, TY, 1); else if (iters == 2) LAUNCH_VEC(TA, TY, 2); else LAUNCH_VEC(TA, TY, 4);
@@ -316,11 +327,17 @@ PH_EXPORT int ph_add_rmsnorm(float* x, const void* add, int add_dtype, int add_s
         auto k = add_rmsnorm_kernel<TA, TY, NT>;                                                                \
         if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
         k<<<n_out, NT, smem, stream>>>(x, (const TA*)add, add_splits, add_split_stride, weight, eps, rows, E,   \
-                                       (TY*)y, write_x);                                                        \
+                                       (TY*)y, write_x, add_scale);                                             \
     } while (0)
     PH_DISPATCH(add_dtype, TA, PH_DISPATCH(y_dtype, TY, LAUNCH(TA, TY)));
 #undef LAUNCH
     return check_launch("add_rmsnorm");
+}
+
+PH_EXPORT int ph_add_rmsnorm(float* x, const void* add, int add_dtype, int add_splits, long long add_split_stride,
+                             const float* weight, float eps, const int32_t* rows, int n_out, int E, void* y,
+                             int y_dtype, int write_x, cudaStream_t stream) {
+    return ph_add_scaled_rmsnorm(x, add, add_dtype, add_splits, add_split_stride, weight, eps, rows, n_out, E, y, y_dtype, write_x, 1.0f, stream);
 }
 
 // x [n_rows, E] float32 += the addends (add_splits partial sums, or none); y = x * weight without the row's factor;

@@ -185,6 +185,7 @@ const CoreKernels& core_kernels() {
     bind(h, "core", "ph_joint_norm_kv_write", g_core.joint_norm_kv_write);
     bind(h, "core", "ph_min_gru_scan", g_core.min_gru_scan);
     bind(h, "core", "ph_pair_sum", g_core.pair_sum);
+    bind(h, "core", "ph_add_scaled_rmsnorm", g_core.add_scaled_rmsnorm);
     bind(h, "core", "ph_scale_softcap", g_core.scale_softcap);
     bind(h, "core", "ph_core_last_error", g_core.last_error);
     g_core_ok = true;

@@ -166,7 +166,7 @@ struct CoreKernels {
     // the same attention on the tensor cores (bfloat16), a tile of 16 rows and all heads per CTA
     int (*attention_talking_mma)(const void*, const void*, const void*, long long, int, const int32_t*, int, const int32_t*, const int32_t*,
                                  const int32_t*, const int32_t*, int, void*, int, int, int, int, int, int, float, float, const float*,
-                                 const float*, const float*, const float*, const void*, long long, cudaStream_t);
+                                 const float*, const float*, const float*, const void*, long long, int, int, float*, float*, cudaStream_t);
     int (*attention_talking_mma_supports)(int, int, int, int);
     int (*joint_norm_kv_write)(const void*, int, int, long long, long long, const float*, const float*, float, const int32_t*, void*, int,
                                void*, void*, int, long long, int, int, int, int, int, int, int, cudaStream_t);
@@ -174,6 +174,9 @@ struct CoreKernels {
     int (*min_gru_scan)(const void*, int, int, long long, long long, const float*, const float*, float*, const int32_t*, const int32_t*,
                         int, int, int, const int32_t*, int, const int32_t*, float*, void*, int, cudaStream_t);
     int (*pair_sum)(const void*, int, int, long long, float, const void*, int, int, long long, float, float*, long long, cudaStream_t);
+    // add_rmsnorm with a factor on the addend
+    int (*add_scaled_rmsnorm)(float*, const void*, int, int, long long, const float*, float, const int32_t*, int, int, void*, int, int, float,
+                              cudaStream_t);
     // logits scaled and softly capped in place
     int (*scale_softcap)(float*, long long, float, float, cudaStream_t);
     const char* (*last_error)(void);

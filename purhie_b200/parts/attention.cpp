@@ -91,6 +91,16 @@ int tc5_splits(int n_tiles, int heads, int max_ctx, int sms, int window) {
     return best;
 }
 
+// CTAs per tile of the kernel that takes all heads of a 16-row tile at once: with fewer tiles than SMs (decoding, a short
+// portion) the keys of a tile are shared so that the device is filled about once; a CTA keeps at least two blocks of 32
+// keys.  It depends on the step's bucketed reach only, so a decode graph replays.
+int tile16_splits(int n_tiles, int max_ctx, int window, int sms) {
+    const int span = window ? std::min(max_ctx, window + 16) : max_ctx;
+    const int blocks = std::max(1, ceil_div(span, 32));
+    if (n_tiles >= sms || blocks < 4) return 1;
+    return std::max(1, std::min({ceil_div(sms, std::max(n_tiles, 1)), blocks / 2, 32}));
+}
+
 // The prompt portions of a step cut into tiles of `rows` rows: segment and first row (within the portion) of
 // each tile (single_rows: a decode row is a tile too, so that every row of the step is in one).  The tiles that look
 // furthest back come first: the grid starts them first and the short ones fill the tail.
@@ -331,10 +341,17 @@ public:
             if (cache.kv_dtype != DType::BF16) throw KernelError("attention_flash: the cache must be bfloat16");
             flash(q, cache, g, ctx, out, abs_positions);
         } else if (use_sink_kernel() && cache.kv_dtype == DType::BF16 && t16.count) {
+            int splits = (int)ctx.option_int("tile16_splits");
+            if (splits < 1) splits = tile16_splits(t16.count, std::max(ctx.decode_max_ctx, ctx.prefill_max_ctx), window_, sm_count());
+            float *part_o = nullptr, *part_ml = nullptr;
+            if (splits > 1) {
+                part_o = ws.get("attn16_part_o", {T, heads_, splits, value_dim_}, DType::F32).as<float>();
+                part_ml = ws.get("attn16_part_ml", {T, heads_, splits, 2}, DType::F32).as<float>();
+            }
             QE_LAUNCH(core, core.attention_talking_mma(q.data, cache.k_base, cache.v_base, cache.page_stride, cache.page_size, g.block_table,
                                                        g.table_width, ctx.seg_start, ctx.seg_ctx_len, t16.data, t16f.data, t16.count, out.data,
                                                        heads_, kv_heads_, head_dim_, value_dim_, window_, 0, (float)scale_, 0.0f, nullptr,
-                                                       nullptr, nullptr, sink_.as<float>(), nullptr, 0, ctx.stream));
+                                                       nullptr, nullptr, sink_.as<float>(), nullptr, 0, splits, T, part_o, part_ml, ctx.stream));
         } else {
             QE_LAUNCH(core, core.attention_generic_sink(q.data, q.code(), cache.k_base, cache.v_base, (int)cache.kv_dtype, cache.page_stride,
                                                         cache.page_size, g.block_table, g.table_width, ctx.row_seg, abs_positions, out.data,
@@ -561,20 +578,28 @@ public:
                                            2.0 * seen * heads_ * (head_dim_ + value_dim_ + (has_mix_ ? heads_ : 0)));
         }
         const StepArray t16 = ctx.array("attention.tiles16.seg"), t16f = ctx.array("attention.tiles16.first");
-        if (use_mma() && cache.kv_dtype == DType::BF16 && t16.count && (!gate || in.tensor.dtype == DType::BF16))
+        if (use_mma() && cache.kv_dtype == DType::BF16 && t16.count && (!gate || in.tensor.dtype == DType::BF16)) {
+            int splits = (int)ctx.option_int("tile16_splits");
+            if (splits < 1) splits = tile16_splits(t16.count, std::max(ctx.decode_max_ctx, ctx.prefill_max_ctx), window_, sm_count());
+            float *part_o = nullptr, *part_ml = nullptr;
+            if (splits > 1) {
+                part_o = ws.get("attn16_part_o", {T, heads_, splits, value_dim_}, DType::F32).as<float>();
+                part_ml = ws.get("attn16_part_ml", {T, heads_, splits, 2}, DType::F32).as<float>();
+            }
             QE_LAUNCH(core, core.attention_talking_mma(q.data, cache.k_base, cache.v_base, cache.page_stride, cache.page_size, g.block_table,
                                                        g.table_width, ctx.seg_start, ctx.seg_ctx_len, t16.data, t16f.data, t16.count, out.data,
                                                        heads_, kv_heads_, head_dim_, value_dim_, window_, 0, (float)scale_, (float)softcap_,
                                                        has_distance_ ? slope_.as<float>() : nullptr, has_distance_ ? rate_.as<float>() : nullptr,
                                                        has_mix_ ? mix_.as<float>() : nullptr, has_sink_ ? sink_.as<float>() : nullptr, gate,
-                                                       gate_stride, ctx.stream));
-        else
+                                                       gate_stride, splits, T, part_o, part_ml, ctx.stream));
+        } else {
             QE_LAUNCH(core, core.attention_talking(q.data, q.code(), cache.k_base, cache.v_base, (int)cache.kv_dtype, cache.page_stride, cache.page_size,
                                                    g.block_table, g.table_width, ctx.row_seg, ctx.position_column(0), out.data, out.code(), T, heads_,
                                                    kv_heads_, head_dim_, value_dim_, window_, 0, (float)scale_, (float)softcap_,
                                                    has_distance_ ? slope_.as<float>() : nullptr, has_distance_ ? rate_.as<float>() : nullptr,
                                                    has_mix_ ? mix_.as<float>() : nullptr, has_sink_ ? sink_.as<float>() : nullptr, gate, gate_code,
                                                    gate_stride, ctx.stream));
+        }
         return o_proj_(out, ctx, "talk_o", DType::F32, T, true, false, ctx.residual, nullptr, &ctx.norm_ahead);
     }
 

@@ -72,14 +72,18 @@ public:
 
     Tensor forward(ResidualStream& stream, StepContext& ctx, const int32_t* rows, int n_rows) override {
         const int n = rows ? n_rows : ctx.T;
-        fold_transformed(stream, ctx);
+        // an addend whose transform is a factor alone is folded in by this norm's own kernel; a norm on the addend, or a
+        // second addend, takes the kernel that knows those first
+        const bool factor_only = stream.has_pending && !stream.has_also && stream.pending.transform.defined() && !stream.pending.transform.weight;
+        if (!factor_only) fold_transformed(stream, ctx);
         Tensor out = ctx.workspace->get(rows ? "normed_rows" : "normed", {n, size_}, compute_dtype);
         const CoreKernels& k = core_kernels();
         const Addend* pend = stream.has_pending ? &stream.pending : nullptr;
         note_norm_cost(stream, n, size_, compute_dtype, !rows);
-        QE_LAUNCH(k, k.add_rmsnorm(stream.x.as<float>(), pend ? pend->tensor.data : nullptr, pend ? pend->tensor.code() : 0,
-                                   pend ? pend->splits : 1, pend ? (long long)ctx.T * size_ : 0, weight_.as<float>(),
-                                   (float)eps_, rows, n, (int)size_, out.data, out.code(), rows ? 0 : 1, ctx.stream));
+        QE_LAUNCH(k, k.add_scaled_rmsnorm(stream.x.as<float>(), pend ? pend->tensor.data : nullptr, pend ? pend->tensor.code() : 0,
+                                          pend ? pend->splits : 1, pend ? (long long)ctx.T * size_ : 0, weight_.as<float>(),
+                                          (float)eps_, rows, n, (int)size_, out.data, out.code(), rows ? 0 : 1,
+                                          pend ? pend->transform.factor : 1.0f, ctx.stream));
         if (!rows) stream.clear();
         return out;
     }

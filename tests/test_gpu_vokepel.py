@@ -462,6 +462,24 @@ def test_the_head_scales_and_caps_the_logits(models):
         close(p.head(xn, cfg["vocab"]), ref, 2e-4)
 
 
+# ---- the tensor-core attention kernel inside whole models, its keys shared by several CTAs ---------------------------
+def test_key_splits_of_the_tile_kernel_agree_with_the_plain_implementation(models):
+    from purhie_b200.engine import StepEntry
+    folder, cfg, w = models["C", "bfloat16"]
+    toks = tokens(300, cfg["vocab"], 6)
+    ref = P.forward(cfg, w, toks)
+    for splits in (1, 3, 0):                                   # whole tiles, three CTAs a tile, the part's own choice
+        eng = engine_for(folder, "bfloat16", max_tokens=1024, step_options={"tile16_splits": splits})
+        close(run_cut(eng, "whole", toks, []), ref, TOL["bfloat16"])
+        close(run_cut(eng, "tail", toks, [2, 250] + [1] * 48), ref, TOL["bfloat16"])
+        eng.add_request("a"); eng.add_request("b")
+        eng.step([StepEntry("a", toks[:200], [])])
+        out = eng.step([StepEntry("a", toks[200:201], [0]), StepEntry("b", toks[:130], list(range(130)))])
+        close(out[:1], ref[200:201], TOL["bfloat16"])
+        close(out[1:], ref[:130], TOL["bfloat16"])
+        eng.close()
+
+
 # ---- generation -----------------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("name,dtype", [("A", "float32"), ("C", "float32")])
 def test_greedy_generation_through_the_entry_point_and_the_scheduler(models, name, dtype):
