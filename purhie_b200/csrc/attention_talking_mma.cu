@@ -35,6 +35,7 @@ struct TalkParams {
     const float* r1; const float* r2; const float* talk; const float* sink;
     const __nv_bfloat16* gate; long long gate_stride;
     int kv_bytes;                 // bytes of the region that holds Q first and the blocks of K and V afterwards
+    int stages;                   // 1 or 2 blocks of keys and values in shared memory
     int splits;                   // CTAs that share a tile's keys (blockIdx.y); above 1 they leave partial results
     float* part_o;                // [T][HQ][splits][DV] float32, unnormalised
     float* part_ml;               // [T][HQ][splits][2]: the exponent's reference (log2 domain) and the sum
@@ -88,7 +89,6 @@ __global__ void __launch_bounds__(MAX_HEADS * 32) attention_talking_mma_kernel(c
         ldmatrix_x4(region + (uint32_t)((h * BM + (lane & 15)) * KP + (ks * 2 + (lane >> 4)) * 16), qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
     __syncthreads();                                          // everybody holds its Q: the region is free for keys
 
-    const uint32_t k_tiles = region, v_tiles = region + (uint32_t)(HKV * BK * KP);
     const int r0 = lane >> 2, r1 = r0 + 8;
     const int z0 = z_first + min(r0, n_rows - 1), z1 = z_first + min(r1, n_rows - 1);
     const int lo0 = first_seen(z0, p.window, p.chunk), lo1 = first_seen(z1, p.window, p.chunk);
@@ -110,26 +110,40 @@ __global__ void __launch_bounds__(MAX_HEADS * 32) attention_talking_mma_kernel(c
         kb_last = min(kb_last, kb_first + per - 1);
     }
     const bool upper = n_rows > 8;                            // rows 8 .. 15 of the tile exist
-    for (int key0 = kb_first * BK; key0 <= kb_last * BK; key0 += BK) {
-        // the block's keys and values of every kv head
-        {
-            constexpr int KC = D / 8, VC = DV / 8;
-            for (int i = threadIdx.x; i < HKV * BK * (KC + VC); i += threads) {
-                const int c = i % (KC + VC), r = (i / (KC + VC)) % BK, gg = i / ((KC + VC) * BK);
-                const int pos = key0 + r;
-                const bool valid = pos >= lo_tile && pos <= z_last;
-                size_t page_at = 0, slot = 0;
-                if (valid) {
-                    page_at = (size_t)table[pos / p.page_size] * p.page_stride;
-                    slot = (size_t)gg * p.page_size + pos % p.page_size;
-                }
-                if (c < KC) cp_async16(k_tiles + (uint32_t)((gg * BK + r) * KP + c * 16), p.k_base + page_at + slot * D + c * 8, valid);
-                else cp_async16(v_tiles + (uint32_t)((gg * BK + r) * VP + (c - KC) * 16), p.v_base + page_at + slot * DV + (c - KC) * 8, valid);
+    // the keys and values of every kv head for the block that starts at key0, into one of the stages
+    const uint32_t stage_bytes = (uint32_t)(HKV * BK * (KP + VP));
+    auto load_block = [&](int key0, int stage) {
+        constexpr int KC = D / 8, VC = DV / 8;
+        const uint32_t kt = region + stage * stage_bytes, vt = kt + (uint32_t)(HKV * BK * KP);
+        for (int i = threadIdx.x; i < HKV * BK * (KC + VC); i += threads) {
+            const int c = i % (KC + VC), r = (i / (KC + VC)) % BK, gg = i / ((KC + VC) * BK);
+            const int pos = key0 + r;
+            const bool valid = pos >= lo_tile && pos <= z_last;
+            size_t page_at = 0, slot = 0;
+            if (valid) {
+                page_at = (size_t)table[pos / p.page_size] * p.page_stride;
+                slot = (size_t)gg * p.page_size + pos % p.page_size;
             }
-            cp_async_commit();
+            if (c < KC) cp_async16(kt + (uint32_t)((gg * BK + r) * KP + c * 16), p.k_base + page_at + slot * D + c * 8, valid);
+            else cp_async16(vt + (uint32_t)((gg * BK + r) * VP + (c - KC) * 16), p.v_base + page_at + slot * DV + (c - KC) * 8, valid);
+        }
+        cp_async_commit();
+    };
+    // two stages: the next block is on its way while this one is worked on; one stage where shared memory has no room for two
+    if (p.stages == 2 && kb_first <= kb_last) load_block(kb_first * BK, 0);
+    for (int kb = kb_first; kb <= kb_last; ++kb) {
+        const int key0 = kb * BK;
+        int stage = 0;
+        if (p.stages == 2) {
+            stage = (kb - kb_first) & 1;
+            if (kb < kb_last) { load_block(key0 + BK, stage ^ 1); cp_async_wait<1>(); }
+            else cp_async_wait<0>();
+        } else {
+            load_block(key0, 0);
             cp_async_wait<0>();
         }
         __syncthreads();
+        const uint32_t k_tiles = region + stage * stage_bytes, v_tiles = k_tiles + (uint32_t)(HKV * BK * KP);
         float s[BK / 8][4];
         warp_qk<D, BK, true>(qf, k_tiles + (uint32_t)(g * BK * KP), 0, s);
 #pragma unroll
@@ -249,15 +263,14 @@ __global__ void attention_talking_merge_kernel(const float* __restrict__ part_o,
     }
 }
 
-size_t smem_need(int HQ, int HKV, int D, int DV) {
-    const size_t qb = (size_t)HQ * BM * (D * 2 + 16), kvb = (size_t)HKV * BK * ((D * 2 + 16) + (DV * 2 + 16));
-    const size_t region = ((qb > kvb ? qb : kvb) + 127) / 128 * 128;
-    return region + ((size_t)HQ * BM * SP + (size_t)HQ * HQ) * sizeof(float);
-}
-size_t region_bytes(int HQ, int HKV, int D, int DV) {
-    const size_t qb = (size_t)HQ * BM * (D * 2 + 16), kvb = (size_t)HKV * BK * ((D * 2 + 16) + (DV * 2 + 16));
+size_t region_bytes(int HQ, int HKV, int D, int DV, int stages) {
+    const size_t qb = (size_t)HQ * BM * (D * 2 + 16), kvb = (size_t)stages * HKV * BK * ((D * 2 + 16) + (DV * 2 + 16));
     return ((qb > kvb ? qb : kvb) + 127) / 128 * 128;
 }
+size_t smem_need(int HQ, int HKV, int D, int DV, int stages) {
+    return region_bytes(HQ, HKV, D, DV, stages) + ((size_t)HQ * BM * SP + (size_t)HQ * HQ) * sizeof(float);
+}
+constexpr size_t SMEM_LIMIT = 227 * 1024;
 bool instantiated(int D, int DV) {
     return (D == DV && (D == 16 || D == 32 || D == 48 || D == 64 || D == 96 || D == 128)) || (D == 64 && DV == 32) || (D == 32 && DV == 64);
 }
@@ -267,7 +280,7 @@ bool instantiated(int D, int DV) {
 // 1 when the kernel takes these sizes (head sizes it is built for, a warp per head, everything in shared memory).
 PH_EXPORT int ph_attention_talking_mma_supports(int HQ, int HKV, int D, int DV) {
     if (HQ < 1 || HKV < 1 || HQ % HKV || HQ > MAX_HEADS || !instantiated(D, DV)) return 0;
-    return smem_need(HQ, HKV, D, DV) <= 227 * 1024 ? 1 : 0;
+    return smem_need(HQ, HKV, D, DV, 1) <= SMEM_LIMIT ? 1 : 0;
 }
 
 // q [T, HQ, D], out [T, HQ * DV] and the cache in bfloat16; the gate's rows (null: none) in bfloat16, gate_stride elements
@@ -295,9 +308,10 @@ PH_EXPORT int ph_attention_talking_mma(const void* q, const void* k_base, const 
     p.seg_start = seg_start; p.seg_ctx_len = seg_ctx_len; p.tile_seg = tile_seg; p.tile_first = tile_first;
     p.out = (__nv_bfloat16*)out; p.HQ = HQ; p.HKV = HKV; p.window = window; p.chunk = chunk; p.scale = scale; p.cap = cap;
     p.r1 = r1; p.r2 = r2; p.talk = talk; p.sink = sink; p.gate = (const __nv_bfloat16*)gate; p.gate_stride = gate_stride;
-    p.kv_bytes = (int)region_bytes(HQ, HKV, D, DV);
+    p.stages = smem_need(HQ, HKV, D, DV, 2) <= SMEM_LIMIT ? 2 : 1;
+    p.kv_bytes = (int)region_bytes(HQ, HKV, D, DV, p.stages);
     p.splits = splits; p.part_o = part_o; p.part_ml = part_ml;
-    const size_t smem = smem_need(HQ, HKV, D, DV);
+    const size_t smem = smem_need(HQ, HKV, D, DV, p.stages);
 #define CASE(DD, VV)                                                                                                      \
     if (D == DD && DV == VV) {                                                                                            \
         auto kern = attention_talking_mma_kernel<DD, VV>;                                                                 \

@@ -97,8 +97,8 @@ int tc5_splits(int n_tiles, int heads, int max_ctx, int sms, int window) {
 int tile16_splits(int n_tiles, int max_ctx, int window, int sms) {
     const int span = window ? std::min(max_ctx, window + 16) : max_ctx;
     const int blocks = std::max(1, ceil_div(span, 32));
-    if (n_tiles >= sms || blocks < 4) return 1;
-    return std::max(1, std::min({ceil_div(sms, std::max(n_tiles, 1)), blocks / 2, 32}));
+    if (2 * n_tiles > sms || blocks < 4) return 1;
+    return std::max(1, std::min({sms / std::max(n_tiles, 1), blocks / 2, 32}));
 }
 
 // The prompt portions of a step cut into tiles of `rows` rows: segment and first row (within the portion) of
