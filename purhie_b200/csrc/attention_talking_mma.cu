@@ -171,6 +171,7 @@ __global__ void __launch_bounds__(MAX_HEADS * 32) attention_talking_mma_kernel(c
             for (int nt = 0; nt < BK / 8; ++nt)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) s[nt][i] = 0.0f;
+#pragma unroll 4
             for (int j = 0; j < HQ; ++j) {
                 const float w = tk[h * HQ + j];
 #pragma unroll
@@ -281,6 +282,15 @@ bool instantiated(int D, int DV) {
 PH_EXPORT int ph_attention_talking_mma_supports(int HQ, int HKV, int D, int DV) {
     if (HQ < 1 || HKV < 1 || HQ % HKV || HQ > MAX_HEADS || !instantiated(D, DV)) return 0;
     return smem_need(HQ, HKV, D, DV, 1) <= SMEM_LIMIT ? 1 : 0;
+}
+
+// CTAs of the kernel that one SM holds at these sizes (registers: 128 a thread; shared memory), 0 when it does not take them.
+PH_EXPORT int ph_attention_talking_mma_ctas_per_sm(int HQ, int HKV, int D, int DV) {
+    if (!ph_attention_talking_mma_supports(HQ, HKV, D, DV)) return 0;
+    const int stages = smem_need(HQ, HKV, D, DV, 2) <= SMEM_LIMIT ? 2 : 1;
+    const int by_regs = 65536 / (128 * HQ * 32), by_smem = (int)(SMEM_LIMIT / (smem_need(HQ, HKV, D, DV, stages) + 1024));
+    const int n = by_regs < by_smem ? by_regs : by_smem;
+    return n < 1 ? 1 : n;
 }
 
 // q [T, HQ, D], out [T, HQ * DV] and the cache in bfloat16; the gate's rows (null: none) in bfloat16, gate_stride elements

@@ -90,8 +90,8 @@ template <> struct Vec4<__nv_bfloat16> {
 // rows it is the number of resident rows per SM that keeps the memory busy.
 constexpr int MANY_PARTS_IN_FLIGHT = 12;
 
-template <typename TA, typename TY, int MAX_IT, int PARTS_IN_FLIGHT>
-__global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const TA* __restrict__ add, int add_splits,
+template <typename TA, typename TY, int MAX_IT, int PARTS_IN_FLIGHT, bool SCALED>
+__device__ __forceinline__ void add_rmsnorm_vec_body(float* __restrict__ x, const TA* __restrict__ add, int add_splits,
                                        long long add_split_stride, const float* __restrict__ weight, float eps,
                                        const int32_t* __restrict__ rows, int E, TY* __restrict__ y, int write_x, float add_scale) {
     __shared__ float scratch[128];
@@ -118,8 +118,8 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const TA* __restri
             float4 acc = Vec4<float>::load(xr + i);
             if (add) {
                 const TA* a = add + (size_t)t * E + i;
-                const float4 base = acc;
-                if (add_scale != 1.0f) acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);   // the addend is summed alone, then scaled
+                float4 base = acc;
+                if (SCALED) acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);              // the addend is summed alone, then scaled
                 for (int s0 = 0; s0 < add_splits; s0 += PARTS_IN_FLIGHT) {      // loads in flight, added in order
                     float4 u[PARTS_IN_FLIGHT];
 #pragma unroll
@@ -130,7 +130,7 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const TA* __restri
                     for (int j = 0; j < PARTS_IN_FLIGHT; ++j)
                         if (s0 + j < add_splits) { acc.x += u[j].x; acc.y += u[j].y; acc.z += u[j].z; acc.w += u[j].w; }
                 }
-                if (add_scale != 1.0f)
+                if (SCALED)
                     acc = make_float4(base.x + add_scale * acc.x, base.y + add_scale * acc.y, base.z + add_scale * acc.z, base.w + add_scale * acc.w);
                 if (write_x) Vec4<float>::store(xr + i, acc);
             }
@@ -160,6 +160,21 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const TA* __restri
             Vec4<TY>::store(yr + i, make_float4(v[it].x * inv * w[it].x, v[it].y * inv * w[it].y, v[it].z * inv * w[it].z,
                                                 v[it].w * inv * w[it].w));
     }
+}
+
+template <typename TA, typename TY, int MAX_IT, int PARTS_IN_FLIGHT>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const TA* __restrict__ add, int add_splits, long long add_split_stride,
+                                       const float* __restrict__ weight, float eps, const int32_t* __restrict__ rows, int E,
+                                       TY* __restrict__ y, int write_x) {
+    add_rmsnorm_vec_body<TA, TY, MAX_IT, PARTS_IN_FLIGHT, false>(x, add, add_splits, add_split_stride, weight, eps, rows, E, y, write_x, 1.0f);
+}
+// with a factor on the addend; a block of up to 1,024 threads must fit
+template <typename TA, typename TY, int MAX_IT, int PARTS_IN_FLIGHT>
+__global__ void __launch_bounds__(1024)
+add_scaled_rmsnorm_vec_kernel(float* __restrict__ x, const TA* __restrict__ add, int add_splits, long long add_split_stride,
+                              const float* __restrict__ weight, float eps, const int32_t* __restrict__ rows, int E, TY* __restrict__ y,
+                              int write_x, float add_scale) {
+    add_rmsnorm_vec_body<TA, TY, MAX_IT, PARTS_IN_FLIGHT, true>(x, add, add_splits, add_split_stride, weight, eps, rows, E, y, write_x, add_scale);
 }
 
 // The same sum with the norm's weight but without the row's factor: v = x + addends (stored back), y = v * weight in the
@@ -305,13 +320,16 @@ PH_EXPORT int ph_add_scaled_rmsnorm(float* x, const void* add, int add_dtype, in
         const int iters = (E / 4 + threads - 1) / threads;
 #define LAUNCH_VEC(TA, TY, IT)                                                                                          \
         do {                                                                                                            \
-            if (!add || add_splits == 1)                                                                                \
-                launch_overlapped(add_rmsnorm_vec_kernel<TA, TY, IT, 1>, dim3(n_out), dim3(threads), 0, stream, x,      \
+            if (add && add_scale != 1.0f)                                                                               \
+                launch_overlapped(add_scaled_rmsnorm_vec_kernel<TA, TY, IT, 4>, dim3(n_out), dim3(threads), 0, stream, x, \
                                   (const TA*)add, add_splits, add_split_stride, weight, eps, rows, E, (TY*)y, write_x, add_scale); \
+            else if (!add || add_splits == 1)                                                                           \
+                launch_overlapped(add_rmsnorm_vec_kernel<TA, TY, IT, 1>, dim3(n_out), dim3(threads), 0, stream, x,      \
+                                  (const TA*)add, add_splits, add_split_stride, weight, eps, rows, E, (TY*)y, write_x); \
             else                                                                                                        \
                 launch_overlapped(add_rmsnorm_vec_kernel<TA, TY, IT, MANY_PARTS_IN_FLIGHT>, dim3(n_out), dim3(threads), \
                                   0, stream, x, (const TA*)add, add_splits, add_split_stride, weight, eps, rows, E,     \
-                                  (TY*)y, write_x, add_scale);                                                          \
+                                  (TY*)y, write_x);                                                                     \
         } while (0)
         PH_DISPATCH(add_dtype, TA, PH_DISPATCH(y_dtype, TY, {
             if (iters == 1) LAUNCH_VEC(TA, TY, 1); else if (iters == 2) LAUNCH_VEC(TA, TY, 2); else LAUNCH_VEC(TA, TY, 4);

@@ -182,6 +182,7 @@ const CoreKernels& core_kernels() {
     bind(h, "core", "ph_attention_talking", g_core.attention_talking);
     bind(h, "core", "ph_attention_talking_mma", g_core.attention_talking_mma);
     bind(h, "core", "ph_attention_talking_mma_supports", g_core.attention_talking_mma_supports);
+    bind(h, "core", "ph_attention_talking_mma_ctas_per_sm", g_core.attention_talking_mma_ctas_per_sm);
     bind(h, "core", "ph_joint_norm_kv_write", g_core.joint_norm_kv_write);
     bind(h, "core", "ph_min_gru_scan", g_core.min_gru_scan);
     bind(h, "core", "ph_pair_sum", g_core.pair_sum);

@@ -168,6 +168,7 @@ struct CoreKernels {
                                  const int32_t*, const int32_t*, int, void*, int, int, int, int, int, int, float, float, const float*,
                                  const float*, const float*, const float*, const void*, long long, int, int, float*, float*, cudaStream_t);
     int (*attention_talking_mma_supports)(int, int, int, int);
+    int (*attention_talking_mma_ctas_per_sm)(int, int, int, int);
     int (*joint_norm_kv_write)(const void*, int, int, long long, long long, const float*, const float*, float, const int32_t*, void*, int,
                                void*, void*, int, long long, int, int, int, int, int, int, int, cudaStream_t);
     // a minimal gated recurrent unit over the rows of each request; the weighted sum of two mixers' outputs

@@ -91,14 +91,14 @@ int tc5_splits(int n_tiles, int heads, int max_ctx, int sms, int window) {
     return best;
 }
 
-// CTAs per tile of the kernel that takes all heads of a 16-row tile at once: with fewer tiles than SMs (decoding, a short
-// portion) the keys of a tile are shared so that the device is filled about once; a CTA keeps at least two blocks of 32
-// keys.  It depends on the step's bucketed reach only, so a decode graph replays.
-int tile16_splits(int n_tiles, int max_ctx, int window, int sms) {
+// CTAs per tile of the kernel that takes all heads of a 16-row tile at once: with fewer tiles than the device holds CTAs
+// (decoding, a short portion, few heads) the keys of a tile are shared so that every place is filled about once; a CTA
+// keeps at least two blocks of 32 keys.  It depends on the step's bucketed reach only, so a decode graph replays.
+int tile16_splits(int n_tiles, int max_ctx, int window, int places) {
     const int span = window ? std::min(max_ctx, window + 16) : max_ctx;
     const int blocks = std::max(1, ceil_div(span, 32));
-    if (2 * n_tiles > sms || blocks < 4) return 1;
-    return std::max(1, std::min({sms / std::max(n_tiles, 1), blocks / 2, 32}));
+    if (2 * n_tiles > places || blocks < 4) return 1;
+    return std::max(1, std::min({places / std::max(n_tiles, 1), blocks / 2, 32}));
 }
 
 // The prompt portions of a step cut into tiles of `rows` rows: segment and first row (within the portion) of
@@ -342,7 +342,9 @@ public:
             flash(q, cache, g, ctx, out, abs_positions);
         } else if (use_sink_kernel() && cache.kv_dtype == DType::BF16 && t16.count) {
             int splits = (int)ctx.option_int("tile16_splits");
-            if (splits < 1) splits = tile16_splits(t16.count, std::max(ctx.decode_max_ctx, ctx.prefill_max_ctx), window_, sm_count());
+            if (splits < 1)
+                splits = tile16_splits(t16.count, std::max(ctx.decode_max_ctx, ctx.prefill_max_ctx), window_,
+                                       sm_count() * core.attention_talking_mma_ctas_per_sm(heads_, kv_heads_, head_dim_, value_dim_));
             float *part_o = nullptr, *part_ml = nullptr;
             if (splits > 1) {
                 part_o = ws.get("attn16_part_o", {T, heads_, splits, value_dim_}, DType::F32).as<float>();
@@ -352,11 +354,16 @@ public:
                                                        g.table_width, ctx.seg_start, ctx.seg_ctx_len, t16.data, t16f.data, t16.count, out.data,
                                                        heads_, kv_heads_, head_dim_, value_dim_, window_, 0, (float)scale_, 0.0f, nullptr,
                                                        nullptr, nullptr, sink_.as<float>(), nullptr, 0, splits, T, part_o, part_ml, ctx.stream));
-        } else {
+        } else if (has_sink_) {
             QE_LAUNCH(core, core.attention_generic_sink(q.data, q.code(), cache.k_base, cache.v_base, (int)cache.kv_dtype, cache.page_stride,
                                                         cache.page_size, g.block_table, g.table_width, ctx.row_seg, abs_positions, out.data,
                                                         out.code(), T, heads_, kv_heads_, head_dim_, window_, (float)scale_, value_dim_, chunk_, 0,
-                                                        has_sink_ ? sink_.as<float>() : nullptr, ctx.stream));
+                                                        sink_.as<float>(), ctx.stream));
+        } else {
+            QE_LAUNCH(core, core.attention_generic(q.data, q.code(), cache.k_base, cache.v_base, (int)cache.kv_dtype, cache.page_stride,
+                                                   cache.page_size, g.block_table, g.table_width, ctx.row_seg, abs_positions, out.data,
+                                                   out.code(), T, heads_, kv_heads_, head_dim_, window_, (float)scale_, value_dim_, chunk_, 0,
+                                                   ctx.stream));
         }
         return o_proj_(out, ctx, "o_out", DType::F32, T, true, false, ctx.residual, nullptr, &ctx.norm_ahead);
     }
@@ -580,7 +587,9 @@ public:
         const StepArray t16 = ctx.array("attention.tiles16.seg"), t16f = ctx.array("attention.tiles16.first");
         if (use_mma() && cache.kv_dtype == DType::BF16 && t16.count && (!gate || in.tensor.dtype == DType::BF16)) {
             int splits = (int)ctx.option_int("tile16_splits");
-            if (splits < 1) splits = tile16_splits(t16.count, std::max(ctx.decode_max_ctx, ctx.prefill_max_ctx), window_, sm_count());
+            if (splits < 1)
+                splits = tile16_splits(t16.count, std::max(ctx.decode_max_ctx, ctx.prefill_max_ctx), window_,
+                                       sm_count() * core.attention_talking_mma_ctas_per_sm(heads_, kv_heads_, head_dim_, value_dim_));
             float *part_o = nullptr, *part_ml = nullptr;
             if (splits > 1) {
                 part_o = ws.get("attn16_part_o", {T, heads_, splits, value_dim_}, DType::F32).as<float>();

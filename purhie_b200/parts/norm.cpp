@@ -80,10 +80,14 @@ public:
         const CoreKernels& k = core_kernels();
         const Addend* pend = stream.has_pending ? &stream.pending : nullptr;
         note_norm_cost(stream, n, size_, compute_dtype, !rows);
-        QE_LAUNCH(k, k.add_scaled_rmsnorm(stream.x.as<float>(), pend ? pend->tensor.data : nullptr, pend ? pend->tensor.code() : 0,
-                                          pend ? pend->splits : 1, pend ? (long long)ctx.T * size_ : 0, weight_.as<float>(),
-                                          (float)eps_, rows, n, (int)size_, out.data, out.code(), rows ? 0 : 1,
-                                          pend ? pend->transform.factor : 1.0f, ctx.stream));
+        if (factor_only)
+            QE_LAUNCH(k, k.add_scaled_rmsnorm(stream.x.as<float>(), pend->tensor.data, pend->tensor.code(), pend->splits, (long long)ctx.T * size_,
+                                              weight_.as<float>(), (float)eps_, rows, n, (int)size_, out.data, out.code(), rows ? 0 : 1,
+                                              pend->transform.factor, ctx.stream));
+        else
+            QE_LAUNCH(k, k.add_rmsnorm(stream.x.as<float>(), pend ? pend->tensor.data : nullptr, pend ? pend->tensor.code() : 0,
+                                       pend ? pend->splits : 1, pend ? (long long)ctx.T * size_ : 0, weight_.as<float>(),
+                                       (float)eps_, rows, n, (int)size_, out.data, out.code(), rows ? 0 : 1, ctx.stream));
         if (!rows) stream.clear();
         return out;
     }
