@@ -52,6 +52,7 @@ struct BulkParams {
     int n_rows, HQ, HKV, splits, window, chunk;
     float scale_log2;
     int* error_flag;
+    const float* sink;             // [HQ] float32 or null: exp(sink) joins each head's denominator, once per row
 };
 
 struct Item {
@@ -364,6 +365,7 @@ attention_decode_bulk_kernel(const __grid_constant__ CUtensorMap map_kv, const B
                 }
                 const int h = it.g * G + r;
                 if (p.splits == 1) {
+                    if (p.sink) ll += exp2f(p.sink[h] * LOG2E - use);
                     p.out[((size_t)it.t * p.HQ + h) * D + d] = __float2bfloat16_rn(ll == 0.0f ? 0.0f : acc / ll);
                 } else {
                     const size_t slot = ((size_t)it.i * p.HQ + h) * p.splits + it.split;
@@ -378,7 +380,8 @@ attention_decode_bulk_kernel(const __grid_constant__ CUtensorMap map_kv, const B
 
 template <int D>
 __global__ void attention_combine_bulk_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                              const int32_t* __restrict__ row_list, __nv_bfloat16* __restrict__ out, int HQ, int splits) {
+                                              const int32_t* __restrict__ row_list, __nv_bfloat16* __restrict__ out, int HQ, int splits,
+                                              const float* __restrict__ sink) {
     // One block per (row, head), a thread per element of the head.  Lane s of every warp fetches the maximum and sum
     // of split s, so that the weights of 32 splits cost one round trip, and the partial outputs are fetched eight
     // splits at a time; the sums run over the splits in ascending order whatever the block's shape.
@@ -416,6 +419,7 @@ __global__ void attention_combine_bulk_kernel(const float* __restrict__ part_o, 
             }
         }
     }
+    if (sink) ll += exp2f(sink[h] * LOG2E - use);           // the sink counts once, after the splits are merged
     out[((size_t)t * HQ + h) * D + d] = __float2bfloat16_rn(ll == 0.0f ? 0.0f : acc / ll);
 }
 
@@ -489,7 +493,7 @@ int launch_config(const CUtensorMap& mkv, const BulkParams& p, int bytes, int ma
     launch_overlapped(kernel, dim3(grid), dim3(BULK_THREADS), (size_t)bytes, stream, mkv, p);
     if (p.splits > 1)
         launch_overlapped(attention_combine_bulk_kernel<D>, dim3(p.n_rows, p.HQ), dim3(D < 128 ? D : 128), 0, stream,
-                          (const float*)p.part_o, (const float*)p.part_ml, p.row_list, p.out, p.HQ, p.splits);
+                          (const float*)p.part_o, (const float*)p.part_ml, p.row_list, p.out, p.HQ, p.splits, p.sink);
     return check_launch("attention_decode_bulk");
 }
 
@@ -508,12 +512,13 @@ template <int D> int launch_bulk(const CUtensorMap& mkv, const BulkParams& p, in
 }  // namespace
 
 // num_pages: pages of the pool that k_base / v_base belong to (the copy engine needs the extent it may address).
-PH_EXPORT int ph_attention_decode_bulk(const void* q, const void* k_base, const void* v_base, long long page_stride,
-                                       int page_size, int num_pages, const int32_t* block_table, int table_stride,
-                                       const int32_t* row_list, int n_rows, const int32_t* row_seg,
-                                       const int32_t* positions, float* part_o, float* part_ml, void* out, int HQ,
-                                       int HKV, int D, int splits, int window, int chunk, float scale, int max_ctas,
-                                       int* error_flag, cudaStream_t stream) {
+// sink: [HQ] float32 or null.
+PH_EXPORT int ph_attention_decode_bulk_sink(const void* q, const void* k_base, const void* v_base, long long page_stride,
+                                            int page_size, int num_pages, const int32_t* block_table, int table_stride,
+                                            const int32_t* row_list, int n_rows, const int32_t* row_seg,
+                                            const int32_t* positions, float* part_o, float* part_ml, void* out, int HQ,
+                                            int HKV, int D, int splits, int window, int chunk, float scale, int max_ctas,
+                                            int* error_flag, const float* sink, cudaStream_t stream) {
     if (!q || !k_base || !v_base || !block_table || !row_seg || !positions || !out || !error_flag || n_rows < 0 ||
         HQ < 1 || HKV < 1 || HQ % HKV || page_size < 1 || num_pages < 1 || window < 0 || chunk < 0 || splits < 1 ||
         (splits > 1 && (!part_o || !part_ml)))
@@ -543,6 +548,17 @@ PH_EXPORT int ph_attention_decode_bulk(const void* q, const void* k_base, const 
     p.block_table = block_table; p.table_stride = table_stride;
     p.row_list = row_list; p.row_seg = row_seg; p.positions = positions; p.part_o = part_o; p.part_ml = part_ml;
     p.out = (__nv_bfloat16*)out; p.n_rows = n_rows; p.HQ = HQ; p.HKV = HKV; p.splits = splits; p.window = window; p.chunk = chunk;
-    p.scale_log2 = scale * LOG2E; p.error_flag = error_flag;
+    p.scale_log2 = scale * LOG2E; p.error_flag = error_flag; p.sink = sink;
     return D == 64 ? launch_bulk<64>(mkv, p, max_ctas, stream) : launch_bulk<128>(mkv, p, max_ctas, stream);
+}
+
+PH_EXPORT int ph_attention_decode_bulk(const void* q, const void* k_base, const void* v_base, long long page_stride,
+                                       int page_size, int num_pages, const int32_t* block_table, int table_stride,
+                                       const int32_t* row_list, int n_rows, const int32_t* row_seg,
+                                       const int32_t* positions, float* part_o, float* part_ml, void* out, int HQ,
+                                       int HKV, int D, int splits, int window, int chunk, float scale, int max_ctas,
+                                       int* error_flag, cudaStream_t stream) {
+    return ph_attention_decode_bulk_sink(q, k_base, v_base, page_stride, page_size, num_pages, block_table, table_stride, row_list, n_rows,
+                                         row_seg, positions, part_o, part_ml, out, HQ, HKV, D, splits, window, chunk, scale, max_ctas,
+                                         error_flag, nullptr, stream);
 }

@@ -74,6 +74,7 @@ struct Tc5Params {
     int splits;                    // CTAs that share a tile's keys (grid z); > 1: partial results, merged by a second kernel
     float* part_o;                 // [T][HQ][splits][D] unnormalised partial outputs
     float* part_ml;                // [T][HQ][splits][2] the exponent's reference and the sum of each partial
+    const float* sink;             // [HQ] float32 or null: exp(sink) joins each head's denominator, once per row
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -440,6 +441,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
         if (ok && n_blocks > 0) ok = mb::wait(o_full, (n_blocks - 1) & 1, p.error_flag, PH_ERR_WAIT_TC5_SOFTMAX);
         if (ok && p.splits == 1) {
             tc_fence_after();
+            if (p.sink && l != 0.0f) l += exp2f(p.sink[h] * LOG2E - m_ref);      // the sum refers to m_ref; so does the sink's term
             const float inv = l == 0.0f ? 0.0f : 1.0f / l;        // a row with no visible key gives 0; NaN stays NaN
             __nv_bfloat16* dst = p.out + (size_t)(row0 + first + r) * p.HQ * D + (size_t)h * D;
 #pragma unroll
@@ -498,7 +500,8 @@ constexpr int MERGE_MAX = 16;      // most CTAs per tile
 __global__ void __launch_bounds__(128)
 attention_prefill_tc5_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                      const int32_t* __restrict__ seg_start, const int32_t* __restrict__ tile_seg,
-                                     const int32_t* __restrict__ tile_first, __nv_bfloat16* __restrict__ out, int HQ, int splits) {
+                                     const int32_t* __restrict__ tile_first, __nv_bfloat16* __restrict__ out, int HQ, int splits,
+                                     const float* __restrict__ sink) {
     pdl_launch_dependents();
     const int tile = blockIdx.x, h = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int seg = tile_seg[tile], first = tile_first[tile];
@@ -528,6 +531,7 @@ attention_prefill_tc5_combine_kernel(const float* __restrict__ part_o, const flo
         acc.x += c * o[s].x; acc.y += c * o[s].y; acc.z += c * o[s].z; acc.w += c * o[s].w;
         l += c * ls[s];
     }
+    if (sink && l != 0.0f) l += exp2f(sink[h] * LOG2E - m);      // the sink counts once, after the splits are merged
     const float inv = l == 0.0f ? 0.0f : 1.0f / l;        // a row with no visible key gives 0; NaN stays NaN
     __nv_bfloat162 h0 = __floats2bfloat162_rn(acc.x * inv, acc.y * inv), h1 = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
     uint2 v;
@@ -582,12 +586,13 @@ PH_DEFINE_LAST_ERROR(ph_flash5)
 // for few tiles that look far back.  tile_seg / tile_first: the step's prompt portions cut into tiles
 // of 128 rows (segment, first row of the tile within the portion).  num_pages: pages of the pool that k_base /
 // v_base belong to.
-PH_EXPORT int ph_attention_prefill_tc5(const void* q, int T, const void* k_base, const void* v_base, long long page_stride,
-                                       int page_size, int num_pages, const int32_t* block_table, int table_stride,
-                                       const int32_t* seg_start, const int32_t* seg_ctx_len, const int32_t* tile_seg,
-                                       const int32_t* tile_first, int n_tiles, void* out, int HQ, int HKV, int head_dim,
-                                       int window, int chunk, float scale, int splits, float* part_o, float* part_ml,
-                                       int* error_flag, cudaStream_t stream) {
+// sink: [HQ] float32 or null.
+PH_EXPORT int ph_attention_prefill_tc5_sink(const void* q, int T, const void* k_base, const void* v_base, long long page_stride,
+                                            int page_size, int num_pages, const int32_t* block_table, int table_stride,
+                                            const int32_t* seg_start, const int32_t* seg_ctx_len, const int32_t* tile_seg,
+                                            const int32_t* tile_first, int n_tiles, void* out, int HQ, int HKV, int head_dim,
+                                            int window, int chunk, float scale, int splits, float* part_o, float* part_ml,
+                                            int* error_flag, const float* sink, cudaStream_t stream) {
     if (!q || !k_base || !v_base || !block_table || !seg_start || !seg_ctx_len || !tile_seg || !tile_first || !out ||
         !error_flag || T < 1 || n_tiles < 0 || HQ < 1 || HKV < 1 || HQ % HKV || num_pages < 1 || window < 0 || chunk < 0 || !(scale > 0.0f))
         return fail(PH_ERR_ARG, "attention_prefill_tc5: bad arguments (tiles %d, HQ %d, HKV %d)", n_tiles, HQ, HKV);
@@ -620,7 +625,7 @@ PH_EXPORT int ph_attention_prefill_tc5(const void* q, int T, const void* k_base,
     p.block_table = block_table; p.table_stride = table_stride; p.seg_start = seg_start; p.seg_ctx_len = seg_ctx_len;
     p.tile_seg = tile_seg; p.tile_first = tile_first; p.n_tiles = n_tiles; p.out = (__nv_bfloat16*)out;
     p.HQ = HQ; p.HKV = HKV; p.window = window; p.chunk = chunk; p.scale_log2 = scale * LOG2E; p.error_flag = error_flag;
-    p.splits = splits; p.part_o = part_o; p.part_ml = part_ml;
+    p.splits = splits; p.part_o = part_o; p.part_ml = part_ml; p.sink = sink;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(attention_prefill_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
@@ -630,6 +635,17 @@ PH_EXPORT int ph_attention_prefill_tc5(const void* q, int T, const void* k_base,
     launch_overlapped(attention_prefill_tc5_kernel, dim3(HQ, n_tiles, splits), dim3(THREADS), (size_t)SMEM_BYTES, stream, mq, mk, mv, p);
     if (splits > 1)
         launch_overlapped(attention_prefill_tc5_combine_kernel, dim3(n_tiles, HQ, BM / 4), dim3(128), 0, stream,
-                          (const float*)part_o, (const float*)part_ml, seg_start, tile_seg, tile_first, (__nv_bfloat16*)out, HQ, splits);
+                          (const float*)part_o, (const float*)part_ml, seg_start, tile_seg, tile_first, (__nv_bfloat16*)out, HQ, splits, sink);
     return check_launch("attention_prefill_tc5");
+}
+
+PH_EXPORT int ph_attention_prefill_tc5(const void* q, int T, const void* k_base, const void* v_base, long long page_stride,
+                                       int page_size, int num_pages, const int32_t* block_table, int table_stride,
+                                       const int32_t* seg_start, const int32_t* seg_ctx_len, const int32_t* tile_seg,
+                                       const int32_t* tile_first, int n_tiles, void* out, int HQ, int HKV, int head_dim,
+                                       int window, int chunk, float scale, int splits, float* part_o, float* part_ml,
+                                       int* error_flag, cudaStream_t stream) {
+    return ph_attention_prefill_tc5_sink(q, T, k_base, v_base, page_stride, page_size, num_pages, block_table, table_stride, seg_start,
+                                         seg_ctx_len, tile_seg, tile_first, n_tiles, out, HQ, HKV, head_dim, window, chunk, scale, splits,
+                                         part_o, part_ml, error_flag, nullptr, stream);
 }

@@ -169,6 +169,72 @@ __global__ void joint_norm_kv_write_kernel(const TI* __restrict__ rows, int spli
     }
 }
 
+// The same with eight consecutive elements per access (every width a multiple of 8, rows 16-byte aligned): a thread's
+// elements never straddle a head.  The sums of squares are taken per thread over its own elements, then over the block:
+// their order depends on the widths alone.
+template <typename TI, typename TQ, typename TKV>
+__global__ void joint_norm_kv_write_vec_kernel(const TI* __restrict__ rows, int splits, long long split_stride, long long row_width,
+                                               const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
+                                               const int32_t* __restrict__ slot_mapping, TQ* __restrict__ q_out, TKV* __restrict__ k_base,
+                                               TKV* __restrict__ v_base, long long page_stride, int page_size, int HQ, int HKV, int D, int DV,
+                                               int v_from_row) {
+    extern __shared__ float buf[];             // [QW + KW]
+    __shared__ float scratch[32];
+    const int t = blockIdx.x;
+    const int QW = HQ * D, KW = HKV * D;
+    const TI* src = rows + (size_t)t * row_width;
+    float sq = 0.0f, sk = 0.0f;
+    for (int i = threadIdx.x * 8; i < QW + KW; i += blockDim.x * 8) {
+        float v[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+        for (int s = 0; s < splits; ++s) {
+            float u[8];
+            load8(src + (size_t)s * split_stride + i, u);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] += u[j];
+        }
+        float ss = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { buf[i + j] = v[j]; ss += v[j] * v[j]; }
+        if (i < QW) sq += ss; else sk += ss;
+    }
+    const float iq = q_w ? rsqrtf(block_sum_any(sq, scratch) / (float)QW + eps) : 1.0f;
+    const float ik = k_w ? rsqrtf(block_sum_any(sk, scratch) / (float)KW + eps) : 1.0f;
+    __syncthreads();
+    TQ* qo = q_out + (size_t)t * QW;
+    for (int i = threadIdx.x * 8; i < QW; i += blockDim.x * 8) {
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = q_w ? buf[i + j] * iq * q_w[i + j] : buf[i + j];
+        store8(qo + i, v);
+    }
+    if (!slot_mapping) return;
+    const int slot = slot_mapping[t];
+    if (slot < 0) return;
+    const size_t page_at = (size_t)(slot / page_size) * page_stride;
+    const int off = slot % page_size;
+    for (int i = threadIdx.x * 8; i < KW; i += blockDim.x * 8) {
+        const int h = i / D, d = i % D;
+        float raw[8], v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { raw[j] = buf[QW + i + j]; v[j] = k_w ? raw[j] * ik * k_w[i + j] : raw[j]; }
+        store8(k_base + page_at + ((size_t)h * page_size + off) * D + d, v);
+        if (!v_from_row) store8(v_base + page_at + ((size_t)h * page_size + off) * DV + d, raw);
+    }
+    if (v_from_row) {
+        for (int i = threadIdx.x * 8; i < HKV * DV; i += blockDim.x * 8) {
+            const int h = i / DV, d = i % DV;
+            float v[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+            for (int s = 0; s < splits; ++s) {
+                float u[8];
+                load8(src + (size_t)s * split_stride + QW + KW + i, u);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] += u[j];
+            }
+            store8(v_base + page_at + ((size_t)h * page_size + off) * DV + d, v);
+        }
+    }
+}
+
 }  // namespace
 
 // gate: rows of HQ * DV logits, gate_stride elements apart, in gate_dtype (null: no gate).  cap 0: no cap.  r1, r2, talk,
@@ -218,6 +284,21 @@ PH_EXPORT int ph_joint_norm_kv_write(const void* rows, int rows_dtype, int split
     if (smem > 200 * 1024) return fail(PH_ERR_UNSUPPORTED, "joint_norm_kv_write: rows of %d elements do not fit shared memory", (HQ + HKV) * D);
     if (T == 0) return PH_OK;
     const int threads = (HQ + HKV) * D >= 2048 ? 512 : 256;
+    const bool vec = D % 8 == 0 && DV % 8 == 0 && row_width % 8 == 0 && split_stride % 8 == 0 && page_stride % 8 == 0 &&
+                     (((uintptr_t)rows | (uintptr_t)q_out | (uintptr_t)k_base | (uintptr_t)v_base) % 32) == 0;
+    if (vec) {
+        const int vthreads = (HQ + HKV) * D / 8 >= 256 ? 256 : 128;
+#define LAUNCH_VEC(TI, TQ, TKV)                                                                                                    \
+    do {                                                                                                                           \
+        auto kern = joint_norm_kv_write_vec_kernel<TI, TQ, TKV>;                                                                   \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                  \
+        kern<<<T, vthreads, smem, stream>>>((const TI*)rows, splits, split_stride, row_width, q_w, k_w, eps, slot_mapping, (TQ*)q_out, \
+                                            (TKV*)k_base, (TKV*)v_base, page_stride, page_size, HQ, HKV, D, DV, v_from_row);       \
+    } while (0)
+        PH_DISPATCH(rows_dtype, TI, PH_DISPATCH(q_dtype, TQ, PH_DISPATCH(kv_dtype, TKV, LAUNCH_VEC(TI, TQ, TKV))));
+#undef LAUNCH_VEC
+        return check_launch("joint_norm_kv_write");
+    }
 #define LAUNCH(TI, TQ, TKV)                                                                                                        \
     do {                                                                                                                           \
         auto kern = joint_norm_kv_write_kernel<TI, TQ, TKV>;                                                                       \

@@ -202,6 +202,8 @@ const FlashKernels& flash_kernels() {
     bind(h, "flash", "ph_attention_decode", g_flash.decode);
     bind(h, "flash", "ph_attention_decode_bulk", g_flash.decode_bulk);
     bind(h, "flash", "ph_attention_prefill_tc5", g_flash.prefill_tc5);
+    bind(h, "flash", "ph_attention_decode_bulk_sink", g_flash.decode_bulk_sink);
+    bind(h, "flash", "ph_attention_prefill_tc5_sink", g_flash.prefill_tc5_sink);
     bind(h, "flash", "ph_flash_last_error", g_flash.last_error);
     g_flash_ok = true;
     return g_flash;

@@ -193,6 +193,13 @@ struct FlashKernels {
     int (*prefill_tc5)(const void*, int, const void*, const void*, long long, int, int, const int32_t*, int, const int32_t*,
                        const int32_t*, const int32_t*, const int32_t*, int, void*, int, int, int, int, int, float, int, float*,
                        float*, int*, cudaStream_t);
+    // the two kernels above with a sink ([HQ] float32) in the softmax's denominator
+    int (*decode_bulk_sink)(const void*, const void*, const void*, long long, int, int, const int32_t*, int, const int32_t*, int,
+                            const int32_t*, const int32_t*, float*, float*, void*, int, int, int, int, int, int, float, int, int*,
+                            const float*, cudaStream_t);
+    int (*prefill_tc5_sink)(const void*, int, const void*, const void*, long long, int, int, const int32_t*, int, const int32_t*,
+                            const int32_t*, const int32_t*, const int32_t*, int, void*, int, int, int, int, int, float, int, float*,
+                            float*, int*, const float*, cudaStream_t);
     const char* (*last_error)(void);
 };
 // attention over cached latent rows on the tensor cores (latent_attention_mma.cu)

@@ -248,8 +248,9 @@ public:
     bool use_flash() const {
         if (compute_dtype != DType::BF16 || attention_ == "generic") return false;
         const int group = heads_ / kv_heads_;
-        // (the tensor-core kernels know no sink)
-        const bool ok = (head_dim_ == 64 || head_dim_ == 128) && value_dim_ == head_dim_ && group >= 1 && group <= 16 && !has_sink_;
+        // (of the tensor-core kernels the tcgen05 prompt kernel and the TMA decode kernel know sinks: heads of 128)
+        const bool ok = (head_dim_ == 64 || head_dim_ == 128) && value_dim_ == head_dim_ && group >= 1 && group <= 16 &&
+                        (!has_sink_ || head_dim_ == 128);
         if (!ok && attention_ == "flash")
             throw KernelError("the flash attention kernels do not take head_dim " + std::to_string(head_dim_) + " with " +
                               std::to_string(group) + " query heads per kv head");
@@ -337,7 +338,11 @@ public:
                                            2.0 * seen * heads_ * (head_dim_ + value_dim_));
         }
         const StepArray t16 = ctx.array("attention.tiles16.seg"), t16f = ctx.array("attention.tiles16.first");
-        if (use_flash()) {
+        // a sink rides in the tcgen05 prompt kernel and the TMA decode kernel only: pages they take, and no other choice by option
+        const bool pages_ok = (cache.page_size == 8 || cache.page_size == 16 || cache.page_size == 32 || cache.page_size == 64) && cache.num_pages > 0;
+        const bool sink_ok = !has_sink_ || (pages_ok && ctx.option("prefill_kernel") != "mma_sync" && ctx.option("decode_kernel") != "cp_async" &&
+                                            ctx.option("sink_kernel") != "tile");
+        if (use_flash() && sink_ok) {
             if (cache.kv_dtype != DType::BF16) throw KernelError("attention_flash: the cache must be bfloat16");
             flash(q, cache, g, ctx, out, abs_positions);
         } else if (use_sink_kernel() && cache.kv_dtype == DType::BF16 && t16.count) {
@@ -385,11 +390,18 @@ private:
                 part_o = ws.get("attn_tile_part_o", {ctx.T, heads_, splits, head_dim_}, DType::F32).as<float>();
                 part_ml = ws.get("attn_tile_part_ml", {ctx.T, heads_, splits, 2}, DType::F32).as<float>();
             }
-            QE_LAUNCH(f, f.prefill_tc5(q.data, ctx.T, cache.k_base, cache.v_base, cache.page_stride, cache.page_size, cache.num_pages,
-                                       g.block_table, g.table_width, ctx.seg_start, ctx.seg_ctx_len, t128.data, t128f.data, t128.count,
-                                       out.data, heads_, kv_heads_, head_dim_, window_, chunk_, (float)scale_, splits, part_o, part_ml,
-                                       ctx.attention_error, ctx.stream));
+            if (has_sink_)
+                QE_LAUNCH(f, f.prefill_tc5_sink(q.data, ctx.T, cache.k_base, cache.v_base, cache.page_stride, cache.page_size, cache.num_pages,
+                                                g.block_table, g.table_width, ctx.seg_start, ctx.seg_ctx_len, t128.data, t128f.data, t128.count,
+                                                out.data, heads_, kv_heads_, head_dim_, window_, chunk_, (float)scale_, splits, part_o, part_ml,
+                                                ctx.attention_error, sink_.as<float>(), ctx.stream));
+            else
+                QE_LAUNCH(f, f.prefill_tc5(q.data, ctx.T, cache.k_base, cache.v_base, cache.page_stride, cache.page_size, cache.num_pages,
+                                           g.block_table, g.table_width, ctx.seg_start, ctx.seg_ctx_len, t128.data, t128f.data, t128.count,
+                                           out.data, heads_, kv_heads_, head_dim_, window_, chunk_, (float)scale_, splits, part_o, part_ml,
+                                           ctx.attention_error, ctx.stream));
         } else if (t64.count) {
+            if (has_sink_) throw Error(kInvalidState, "attention: the tiled prompt kernel knows no sink");
             QE_LAUNCH(f, f.prefill(q.data, cache.k_base, cache.v_base, cache.page_stride, cache.page_size, g.block_table, g.table_width,
                                    ctx.seg_start, ctx.seg_ctx_len, t64.data, t64f.data, t64.count, out.data, heads_, kv_heads_,
                                    head_dim_, window_, chunk_, (float)scale_, ctx.stream));
@@ -407,10 +419,17 @@ private:
             part_o = ws.get("attn_part_o", {n, heads_, splits, head_dim_}, DType::F32).as<float>();
             part_ml = ws.get("attn_part_ml", {n, heads_, splits, 2}, DType::F32).as<float>();
         }
-        if (bulk)
+        if (bulk && has_sink_)
+            QE_LAUNCH(f, f.decode_bulk_sink(q.data, cache.k_base, cache.v_base, cache.page_stride, cache.page_size, cache.num_pages, g.block_table,
+                                            g.table_width, ctx.decode_rows, n, ctx.row_seg, positions, part_o, part_ml, out.data, heads_,
+                                            kv_heads_, head_dim_, splits, window_, chunk_, (float)scale_, 0, ctx.attention_error,
+                                            sink_.as<float>(), ctx.stream));
+        else if (bulk)
             QE_LAUNCH(f, f.decode_bulk(q.data, cache.k_base, cache.v_base, cache.page_stride, cache.page_size, cache.num_pages, g.block_table,
                                        g.table_width, ctx.decode_rows, n, ctx.row_seg, positions, part_o, part_ml, out.data, heads_,
                                        kv_heads_, head_dim_, splits, window_, chunk_, (float)scale_, 0, ctx.attention_error, ctx.stream));
+        else if (has_sink_)
+            throw Error(kInvalidState, "attention: the cp.async decode kernel knows no sink");
         else
             QE_LAUNCH(f, f.decode(q.data, cache.k_base, cache.v_base, cache.page_stride, cache.page_size, g.block_table, g.table_width,
                                   ctx.decode_rows, n, ctx.row_seg, positions, part_o, part_ml, out.data, heads_, kv_heads_, head_dim_,
