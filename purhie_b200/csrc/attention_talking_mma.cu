@@ -22,11 +22,13 @@ using namespace ph_attn;
 constexpr int BM = 16;            // query rows of a tile
 constexpr int BK = 32;            // keys of a block
 constexpr int SP = 40;            // floats between two rows of the exchanged scores (8-byte accesses miss each other's banks)
+constexpr int BIAS_N = 48;        // distances row - key + 31 of a block: 0 .. 46
 constexpr int MAX_HEADS = 16;      // a warp per head, and a thread keeps its head's Q and O in registers
 
 struct TalkParams {
     const __nv_bfloat16* q; const __nv_bfloat16* k_base; const __nv_bfloat16* v_base;
     long long page_stride; int page_size;
+    int page_shift;               // log2(page_size) when it is a power of two, else -1
     const int32_t* block_table; int table_stride;
     const int32_t* seg_start; const int32_t* seg_ctx_len; const int32_t* tile_seg; const int32_t* tile_first;
     __nv_bfloat16* out;
@@ -41,13 +43,12 @@ struct TalkParams {
     float* part_ml;               // [T][HQ][splits][2]: the exponent's reference (log2 domain) and the sum
 };
 
-// tanh and ln(1 + x) from the hardware's exponential and logarithm: a few float32 operations each with errors near 1e-6,
-// far below what the bfloat16 weights of the softmax keep
+// tanh from the hardware's exponential: a few float32 operations with an error near 1e-6, far below what the bfloat16
+// weights of the softmax keep
 __device__ __forceinline__ float fast_tanh(float x) {
     const float e = __expf(-2.0f * fabsf(x));
     return copysignf(__fdividef(1.0f - e, 1.0f + e), x);
 }
-__device__ __forceinline__ float fast_log1p(float x) { return x < 0.25f ? log1pf(x) : __logf(1.0f + x); }
 
 template <int D, int DV>
 __global__ void __launch_bounds__(MAX_HEADS * 32) attention_talking_mma_kernel(const TalkParams p) {
@@ -59,6 +60,7 @@ __global__ void __launch_bounds__(MAX_HEADS * 32) attention_talking_mma_kernel(c
     const uint32_t region = smem_u32(smem);
     float* sc = reinterpret_cast<float*>(smem + p.kv_bytes);  // [HQ][BM][SP]
     float* tk = sc + (size_t)HQ * BM * SP;                    // [HQ][HQ]
+    float* bias = tk + (size_t)HQ * HQ + (size_t)h * BIAS_N;  // this head's distance bias for the block's 47 distances
 
     const int tile = blockIdx.x;
     const int seg = p.tile_seg[tile], first = p.tile_first[tile];
@@ -92,7 +94,7 @@ __global__ void __launch_bounds__(MAX_HEADS * 32) attention_talking_mma_kernel(c
     const int r0 = lane >> 2, r1 = r0 + 8;
     const int z0 = z_first + min(r0, n_rows - 1), z1 = z_first + min(r1, n_rows - 1);
     const int lo0 = first_seen(z0, p.window, p.chunk), lo1 = first_seen(z1, p.window, p.chunk);
-    const int lo_tile = first_seen(z_first, p.window, p.chunk);
+    const int lo_tile = first_seen(z_first, p.window, p.chunk), lo_last = first_seen(z_last, p.window, p.chunk);
     const float b1 = p.r1 ? p.r1[h] : 0.0f, b2 = p.r2 ? p.r2[h] : 0.0f;
 
     float o[DV / 8][4];
@@ -121,8 +123,9 @@ __global__ void __launch_bounds__(MAX_HEADS * 32) attention_talking_mma_kernel(c
             const bool valid = pos >= lo_tile && pos <= z_last;
             size_t page_at = 0, slot = 0;
             if (valid) {
-                page_at = (size_t)table[pos / p.page_size] * p.page_stride;
-                slot = (size_t)gg * p.page_size + pos % p.page_size;
+                const int page = p.page_shift >= 0 ? pos >> p.page_shift : pos / p.page_size;
+                page_at = (size_t)table[page] * p.page_stride;
+                slot = (size_t)gg * p.page_size + (pos - page * p.page_size);
             }
             if (c < KC) cp_async16(kt + (uint32_t)((gg * BK + r) * KP + c * 16), p.k_base + page_at + slot * D + c * 8, valid);
             else cp_async16(vt + (uint32_t)((gg * BK + r) * VP + (c - KC) * 16), p.v_base + page_at + slot * DV + (c - KC) * 8, valid);
@@ -144,19 +147,23 @@ __global__ void __launch_bounds__(MAX_HEADS * 32) attention_talking_mma_kernel(c
         }
         __syncthreads();
         const uint32_t k_tiles = region + stage * stage_bytes, v_tiles = k_tiles + (uint32_t)(HKV * BK * KP);
+        if (p.r1) {
+            // the bias depends on the distance alone: row - key takes 47 values in a block, a lane makes two of them
+            __syncwarp();
+            for (int idx = lane; idx < BIAS_N - 1; idx += 32) bias[idx] = b1 * log1pf(b2 * (float)max(z_first - key0 + idx - (BK - 1), 0));
+            __syncwarp();
+        }
         float s[BK / 8][4];
         warp_qk<D, BK, true>(qf, k_tiles + (uint32_t)(g * BK * KP), 0, s);
+        const float inv_cap = p.cap > 0.0f ? 1.0f / p.cap : 0.0f;
 #pragma unroll
         for (int nt = 0; nt < BK / 8; ++nt)
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 if (i >= 2 && !upper) continue;              // a tile of few rows (a decode row) skips the copies of its last row
                 float v = s[nt][i] * p.scale;
-                if (p.cap > 0.0f) v = p.cap * fast_tanh(__fdividef(v, p.cap));
-                if (p.r1) {
-                    const int dist = (i < 2 ? z0 : z1) - (key0 + nt * 8 + (lane & 3) * 2 + (i & 1));
-                    v -= b1 * fast_log1p(b2 * (float)max(dist, 0));
-                }
+                if (p.cap > 0.0f) v = p.cap * fast_tanh(v * inv_cap);
+                if (p.r1) v -= bias[(i < 2 ? r0 : r1) - (nt * 8 + (lane & 3) * 2 + (i & 1)) + (BK - 1)];
                 s[nt][i] = v;
             }
         if (p.talk) {
@@ -167,26 +174,34 @@ __global__ void __launch_bounds__(MAX_HEADS * 32) attention_talking_mma_kernel(c
                 *reinterpret_cast<float2*>(sc + ((size_t)h * BM + r1) * SP + c) = make_float2(s[nt][2], s[nt][3]);
             }
             __syncthreads();
+            // the mix in packed pairs: a thread's two neighbouring columns are one 64-bit accumulator
+            unsigned long long acc[BK / 8][2];
 #pragma unroll
-            for (int nt = 0; nt < BK / 8; ++nt)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) s[nt][i] = 0.0f;
+            for (int nt = 0; nt < BK / 8; ++nt) acc[nt][0] = acc[nt][1] = 0ull;
 #pragma unroll 4
             for (int j = 0; j < HQ; ++j) {
-                const float w = tk[h * HQ + j];
+                unsigned long long ww;
+                asm("mov.b64 %0, {%1, %1};" : "=l"(ww) : "f"(tk[h * HQ + j]));
 #pragma unroll
                 for (int nt = 0; nt < BK / 8; ++nt) {
                     const int c = nt * 8 + (lane & 3) * 2;
-                    const float2 a = *reinterpret_cast<const float2*>(sc + ((size_t)j * BM + r0) * SP + c);
-                    s[nt][0] += w * a.x; s[nt][1] += w * a.y;
+                    const unsigned long long a = *reinterpret_cast<const unsigned long long*>(sc + ((size_t)j * BM + r0) * SP + c);
+                    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc[nt][0]) : "l"(ww), "l"(a));
                     if (upper) {
-                        const float2 b = *reinterpret_cast<const float2*>(sc + ((size_t)j * BM + r1) * SP + c);
-                        s[nt][2] += w * b.x; s[nt][3] += w * b.y;
+                        const unsigned long long b = *reinterpret_cast<const unsigned long long*>(sc + ((size_t)j * BM + r1) * SP + c);
+                        asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc[nt][1]) : "l"(ww), "l"(b));
                     }
                 }
             }
+#pragma unroll
+            for (int nt = 0; nt < BK / 8; ++nt) {
+                asm("mov.b64 {%0, %1}, %2;" : "=f"(s[nt][0]), "=f"(s[nt][1]) : "l"(acc[nt][0]));
+                asm("mov.b64 {%0, %1}, %2;" : "=f"(s[nt][2]), "=f"(s[nt][3]) : "l"(acc[nt][1]));
+            }
         }
-        softmax_update<DV, BK>(s, key0, z0, z1, lo0, lo1, true, LOG2E, m, l, o);
+        // masks only where the block touches the diagonal or the window's edge of one of the tile's rows
+        const bool need_mask = key0 + BK - 1 > z_first || key0 < lo_last;
+        softmax_update<DV, BK>(s, key0, z0, z1, lo0, lo1, need_mask, LOG2E, m, l, o);
         warp_pv<DV, BK, true>(s, v_tiles + (uint32_t)(g * BK * VP), 0, o);
         __syncthreads();                                      // scores and tiles are read before the next block overwrites them
     }
@@ -269,7 +284,7 @@ size_t region_bytes(int HQ, int HKV, int D, int DV, int stages) {
     return ((qb > kvb ? qb : kvb) + 127) / 128 * 128;
 }
 size_t smem_need(int HQ, int HKV, int D, int DV, int stages) {
-    return region_bytes(HQ, HKV, D, DV, stages) + ((size_t)HQ * BM * SP + (size_t)HQ * HQ) * sizeof(float);
+    return region_bytes(HQ, HKV, D, DV, stages) + ((size_t)HQ * BM * SP + (size_t)HQ * HQ + (size_t)HQ * BIAS_N) * sizeof(float);
 }
 constexpr size_t SMEM_LIMIT = 227 * 1024;
 bool instantiated(int D, int DV) {
@@ -314,7 +329,10 @@ PH_EXPORT int ph_attention_talking_mma(const void* q, const void* k_base, const 
     if (n_tiles == 0) return PH_OK;
     TalkParams p;
     p.q = (const __nv_bfloat16*)q; p.k_base = (const __nv_bfloat16*)k_base; p.v_base = (const __nv_bfloat16*)v_base;
-    p.page_stride = page_stride; p.page_size = page_size; p.block_table = block_table; p.table_stride = table_stride;
+    p.page_stride = page_stride; p.page_size = page_size;
+    p.page_shift = -1;
+    for (int b = 0; b < 30; ++b) if ((1 << b) == page_size) p.page_shift = b;
+ p.block_table = block_table; p.table_stride = table_stride;
     p.seg_start = seg_start; p.seg_ctx_len = seg_ctx_len; p.tile_seg = tile_seg; p.tile_first = tile_first;
     p.out = (__nv_bfloat16*)out; p.HQ = HQ; p.HKV = HKV; p.window = window; p.chunk = chunk; p.scale = scale; p.cap = cap;
     p.r1 = r1; p.r2 = r2; p.talk = talk; p.sink = sink; p.gate = (const __nv_bfloat16*)gate; p.gate_stride = gate_stride;
