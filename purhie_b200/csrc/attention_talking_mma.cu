@@ -12,7 +12,12 @@
 // (running maximum and sum per row) and O_h += P_h V_kv(h) on the tensor cores with P rounded to bfloat16, as in the
 // other tensor-core attention kernels.  The sink joins the denominator at the end; the gate multiplies the output.
 // Q tiles of all heads pass through the shared memory that the keys use afterwards.
+// More than 16 heads (up to 32): a cluster of two CTAs takes a tile, each CTA half of the heads with their kv heads; the
+// scores of the other half are read from the partner's shared memory (distributed shared memory), and the two barriers of
+// a block become barriers of the cluster.  Both CTAs walk the same key blocks, so they meet the same barriers.
 #include "attention_mma.cuh"
+
+#include <cooperative_groups.h>
 
 namespace {
 
@@ -37,6 +42,7 @@ struct TalkParams {
     const float* r1; const float* r2; const float* talk; const float* sink;
     const __nv_bfloat16* gate; long long gate_stride;
     int kv_bytes;                 // bytes of the region that holds Q first and the blocks of K and V afterwards
+    int pair;                     // 1: a cluster of two CTAs per tile, each with half of the heads
     int stages;                   // 1 or 2 blocks of keys and values in shared memory
     int splits;                   // CTAs that share a tile's keys (blockIdx.y); above 1 they leave partial results
     float* part_o;                // [T][HQ][splits][DV] float32, unnormalised
@@ -54,15 +60,21 @@ template <int D, int DV>
 __global__ void __launch_bounds__(MAX_HEADS * 32) attention_talking_mma_kernel(const TalkParams p) {
     constexpr int KP = D * 2 + 16, VP = DV * 2 + 16;          // bytes between two rows of a K (Q) and of a V tile
     extern __shared__ __align__(128) uint8_t smem[];
-    const int HQ = p.HQ, HKV = p.HKV;
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    const int rank = p.pair ? (int)cluster.block_rank() : 0;
+    const int HA = p.HQ;                                      // all heads: what a score is mixed over, and the output's stride
+    const int HQ = p.pair ? p.HQ / 2 : p.HQ, HKV = p.pair ? p.HKV / 2 : p.HKV;      // this CTA's heads and kv heads
+    const int h0 = rank * HQ, kv0 = rank * HKV;               // the first of them
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, threads = blockDim.x;
-    const int h = warp, g = h / (HQ / HKV);
+    const int h = warp, g = h / (HQ / HKV);                   // within this CTA
     const uint32_t region = smem_u32(smem);
-    float* sc = reinterpret_cast<float*>(smem + p.kv_bytes);  // [HQ][BM][SP]
-    float* tk = sc + (size_t)HQ * BM * SP;                    // [HQ][HQ]
-    float* bias = tk + (size_t)HQ * HQ + (size_t)h * BIAS_N;  // this head's distance bias for the block's 47 distances
+    float* sc = reinterpret_cast<float*>(smem + p.kv_bytes);  // [HQ][BM][SP]: this CTA's heads' scores
+    float* tk = sc + (size_t)HQ * BM * SP;                    // [HQ][HA]: this CTA's rows of the mix
+    float* bias = tk + (size_t)HQ * HA + (size_t)h * BIAS_N;  // this head's distance bias for the block's 47 distances
+    const float* sc_other = p.pair ? cluster.map_shared_rank(sc, rank ^ 1) : sc;      // the partner's scores
 
-    const int tile = blockIdx.x;
+    const int tile = p.pair ? blockIdx.x / 2 : blockIdx.x;
     const int seg = p.tile_seg[tile], first = p.tile_first[tile];
     const int row0 = p.seg_start[seg], q_len = p.seg_start[seg + 1] - row0;
     const int ctx_len = p.seg_ctx_len[seg];
@@ -76,13 +88,13 @@ __global__ void __launch_bounds__(MAX_HEADS * 32) attention_talking_mma_kernel(c
         for (int i = threadIdx.x; i < HQ * BM * CPR; i += threads) {
             const int c = i % CPR, r = (i / CPR) % BM, hh = i / (CPR * BM);
             const bool valid = r < n_rows;
-            const __nv_bfloat16* src = p.q + ((size_t)(row0 + first + (valid ? r : 0)) * HQ + hh) * D + c * 8;
+            const __nv_bfloat16* src = p.q + ((size_t)(row0 + first + (valid ? r : 0)) * HA + h0 + hh) * D + c * 8;
             cp_async16(region + (uint32_t)((hh * BM + r) * KP + c * 16), src, valid);
         }
         cp_async_commit();
     }
     if (p.talk)
-        for (int i = threadIdx.x; i < HQ * HQ; i += threads) tk[i] = p.talk[i];
+        for (int i = threadIdx.x; i < HQ * HA; i += threads) tk[i] = p.talk[(size_t)h0 * HA + i];
     cp_async_wait<0>();
     __syncthreads();
     uint32_t qf[D / 16][4];
@@ -95,7 +107,7 @@ __global__ void __launch_bounds__(MAX_HEADS * 32) attention_talking_mma_kernel(c
     const int z0 = z_first + min(r0, n_rows - 1), z1 = z_first + min(r1, n_rows - 1);
     const int lo0 = first_seen(z0, p.window, p.chunk), lo1 = first_seen(z1, p.window, p.chunk);
     const int lo_tile = first_seen(z_first, p.window, p.chunk), lo_last = first_seen(z_last, p.window, p.chunk);
-    const float b1 = p.r1 ? p.r1[h] : 0.0f, b2 = p.r2 ? p.r2[h] : 0.0f;
+    const float b1 = p.r1 ? p.r1[h0 + h] : 0.0f, b2 = p.r2 ? p.r2[h0 + h] : 0.0f;
 
     float o[DV / 8][4];
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
@@ -125,7 +137,7 @@ __global__ void __launch_bounds__(MAX_HEADS * 32) attention_talking_mma_kernel(c
             if (valid) {
                 const int page = p.page_shift >= 0 ? pos >> p.page_shift : pos / p.page_size;
                 page_at = (size_t)table[page] * p.page_stride;
-                slot = (size_t)gg * p.page_size + (pos - page * p.page_size);
+                slot = (size_t)(kv0 + gg) * p.page_size + (pos - page * p.page_size);
             }
             if (c < KC) cp_async16(kt + (uint32_t)((gg * BK + r) * KP + c * 16), p.k_base + page_at + slot * D + c * 8, valid);
             else cp_async16(vt + (uint32_t)((gg * BK + r) * VP + (c - KC) * 16), p.v_base + page_at + slot * DV + (c - KC) * 8, valid);
@@ -173,22 +185,23 @@ __global__ void __launch_bounds__(MAX_HEADS * 32) attention_talking_mma_kernel(c
                 *reinterpret_cast<float2*>(sc + ((size_t)h * BM + r0) * SP + c) = make_float2(s[nt][0], s[nt][1]);
                 *reinterpret_cast<float2*>(sc + ((size_t)h * BM + r1) * SP + c) = make_float2(s[nt][2], s[nt][3]);
             }
-            __syncthreads();
+            if (p.pair) cluster.sync(); else __syncthreads();
             // the mix in packed pairs: a thread's two neighbouring columns are one 64-bit accumulator
             unsigned long long acc[BK / 8][2];
 #pragma unroll
             for (int nt = 0; nt < BK / 8; ++nt) acc[nt][0] = acc[nt][1] = 0ull;
 #pragma unroll 4
-            for (int j = 0; j < HQ; ++j) {
+            for (int j = 0; j < HA; ++j) {                    // over all heads, in the order of the heads whichever CTA holds them
                 unsigned long long ww;
-                asm("mov.b64 %0, {%1, %1};" : "=l"(ww) : "f"(tk[h * HQ + j]));
+                asm("mov.b64 %0, {%1, %1};" : "=l"(ww) : "f"(tk[h * HA + j]));
+                const float* from = (j >= h0 && j < h0 + HQ) ? sc + (size_t)(j - h0) * BM * SP : sc_other + (size_t)(j - (h0 ? 0 : HQ)) * BM * SP;
 #pragma unroll
                 for (int nt = 0; nt < BK / 8; ++nt) {
                     const int c = nt * 8 + (lane & 3) * 2;
-                    const unsigned long long a = *reinterpret_cast<const unsigned long long*>(sc + ((size_t)j * BM + r0) * SP + c);
+                    const unsigned long long a = *reinterpret_cast<const unsigned long long*>(from + (size_t)r0 * SP + c);
                     asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc[nt][0]) : "l"(ww), "l"(a));
                     if (upper) {
-                        const unsigned long long b = *reinterpret_cast<const unsigned long long*>(sc + ((size_t)j * BM + r1) * SP + c);
+                        const unsigned long long b = *reinterpret_cast<const unsigned long long*>(from + (size_t)r1 * SP + c);
                         asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc[nt][1]) : "l"(ww), "l"(b));
                     }
                 }
@@ -203,16 +216,17 @@ __global__ void __launch_bounds__(MAX_HEADS * 32) attention_talking_mma_kernel(c
         const bool need_mask = key0 + BK - 1 > z_first || key0 < lo_last;
         softmax_update<DV, BK>(s, key0, z0, z1, lo0, lo1, need_mask, LOG2E, m, l, o);
         warp_pv<DV, BK, true>(s, v_tiles + (uint32_t)(g * BK * VP), 0, o);
-        __syncthreads();                                      // scores and tiles are read before the next block overwrites them
+        // scores and tiles are read (the scores by the partner too) before the next block overwrites them
+        if (p.pair && p.talk) cluster.sync(); else __syncthreads();
     }
     if (p.splits > 1) {
         // (reference, sum, unnormalised output) of this CTA's keys; the merge adds the sink and the gate
-        const int T_HQ = HQ;
+        const int T_HQ = HA;
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
             const int r = k ? r1 : r0;
             if (r >= n_rows) continue;
-            const size_t slot = ((size_t)(row0 + first + r) * T_HQ + h) * p.splits + blockIdx.y;
+            const size_t slot = ((size_t)(row0 + first + r) * T_HQ + h0 + h) * p.splits + blockIdx.y;
             if ((lane & 3) == 0) { p.part_ml[slot * 2] = m[k]; p.part_ml[slot * 2 + 1] = l[k]; }
 #pragma unroll
             for (int dt = 0; dt < DV / 8; ++dt) {
@@ -223,7 +237,7 @@ __global__ void __launch_bounds__(MAX_HEADS * 32) attention_talking_mma_kernel(c
         return;
     }
     if (p.sink) {
-        const float sk = p.sink[h] * LOG2E;
+        const float sk = p.sink[h0 + h] * LOG2E;
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
             const float top = fmaxf(m[k], sk), corr = exp2f(m[k] - top);      // m = -inf cannot happen: a row sees itself
@@ -233,7 +247,7 @@ __global__ void __launch_bounds__(MAX_HEADS * 32) attention_talking_mma_kernel(c
         }
     }
     const float inv0 = l[0] == 0.0f ? 0.0f : 1.0f / l[0], inv1 = l[1] == 0.0f ? 0.0f : 1.0f / l[1];
-    const size_t width = (size_t)HQ * DV;
+    const size_t width = (size_t)HA * DV;
 #pragma unroll
     for (int dt = 0; dt < DV / 8; ++dt) {
         const int d = dt * 8 + (lane & 3) * 2;
@@ -244,11 +258,11 @@ __global__ void __launch_bounds__(MAX_HEADS * 32) attention_talking_mma_kernel(c
             const size_t row = (size_t)(row0 + first + r);
             float a = o[dt][2 * k] * (k ? inv1 : inv0), b = o[dt][2 * k + 1] * (k ? inv1 : inv0);
             if (p.gate) {
-                const __nv_bfloat162 gg = *reinterpret_cast<const __nv_bfloat162*>(p.gate + row * p.gate_stride + (size_t)h * DV + d);
+                const __nv_bfloat162 gg = *reinterpret_cast<const __nv_bfloat162*>(p.gate + row * p.gate_stride + (size_t)(h0 + h) * DV + d);
                 a *= 1.0f / (1.0f + expf(-__low2float(gg)));
                 b *= 1.0f / (1.0f + expf(-__high2float(gg)));
             }
-            *(uint32_t*)(p.out + row * width + (size_t)h * DV + d) = pack_bf16(a, b);
+            *(uint32_t*)(p.out + row * width + (size_t)(h0 + h) * DV + d) = pack_bf16(a, b);
         }
     }
 }
@@ -279,12 +293,16 @@ __global__ void attention_talking_merge_kernel(const float* __restrict__ part_o,
     }
 }
 
+// (of one CTA: with more than MAX_HEADS heads a CTA holds half of the heads and kv heads)
+bool paired(int HQ) { return HQ > MAX_HEADS; }
 size_t region_bytes(int HQ, int HKV, int D, int DV, int stages) {
+    if (paired(HQ)) { HQ /= 2; HKV /= 2; }
     const size_t qb = (size_t)HQ * BM * (D * 2 + 16), kvb = (size_t)stages * HKV * BK * ((D * 2 + 16) + (DV * 2 + 16));
     return ((qb > kvb ? qb : kvb) + 127) / 128 * 128;
 }
 size_t smem_need(int HQ, int HKV, int D, int DV, int stages) {
-    return region_bytes(HQ, HKV, D, DV, stages) + ((size_t)HQ * BM * SP + (size_t)HQ * HQ + (size_t)HQ * BIAS_N) * sizeof(float);
+    const int HL = paired(HQ) ? HQ / 2 : HQ;
+    return region_bytes(HQ, HKV, D, DV, stages) + ((size_t)HL * BM * SP + (size_t)HL * HQ + (size_t)HL * BIAS_N) * sizeof(float);
 }
 constexpr size_t SMEM_LIMIT = 227 * 1024;
 bool instantiated(int D, int DV) {
@@ -295,7 +313,8 @@ bool instantiated(int D, int DV) {
 
 // 1 when the kernel takes these sizes (head sizes it is built for, a warp per head, everything in shared memory).
 PH_EXPORT int ph_attention_talking_mma_supports(int HQ, int HKV, int D, int DV) {
-    if (HQ < 1 || HKV < 1 || HQ % HKV || HQ > MAX_HEADS || !instantiated(D, DV)) return 0;
+    if (HQ < 1 || HKV < 1 || HQ % HKV || HQ > 2 * MAX_HEADS || !instantiated(D, DV)) return 0;
+    if (paired(HQ) && (HQ % 2 || HKV % 2)) return 0;          // two CTAs halve the heads and the kv heads
     return smem_need(HQ, HKV, D, DV, 1) <= SMEM_LIMIT ? 1 : 0;
 }
 
@@ -303,7 +322,7 @@ PH_EXPORT int ph_attention_talking_mma_supports(int HQ, int HKV, int D, int DV) 
 PH_EXPORT int ph_attention_talking_mma_ctas_per_sm(int HQ, int HKV, int D, int DV) {
     if (!ph_attention_talking_mma_supports(HQ, HKV, D, DV)) return 0;
     const int stages = smem_need(HQ, HKV, D, DV, 2) <= SMEM_LIMIT ? 2 : 1;
-    const int by_regs = 65536 / (128 * HQ * 32), by_smem = (int)(SMEM_LIMIT / (smem_need(HQ, HKV, D, DV, stages) + 1024));
+    const int by_regs = 65536 / (128 * (paired(HQ) ? HQ / 2 : HQ) * 32), by_smem = (int)(SMEM_LIMIT / (smem_need(HQ, HKV, D, DV, stages) + 1024));
     const int n = by_regs < by_smem ? by_regs : by_smem;
     return n < 1 ? 1 : n;
 }
@@ -336,6 +355,7 @@ PH_EXPORT int ph_attention_talking_mma(const void* q, const void* k_base, const 
     p.seg_start = seg_start; p.seg_ctx_len = seg_ctx_len; p.tile_seg = tile_seg; p.tile_first = tile_first;
     p.out = (__nv_bfloat16*)out; p.HQ = HQ; p.HKV = HKV; p.window = window; p.chunk = chunk; p.scale = scale; p.cap = cap;
     p.r1 = r1; p.r2 = r2; p.talk = talk; p.sink = sink; p.gate = (const __nv_bfloat16*)gate; p.gate_stride = gate_stride;
+    p.pair = paired(HQ) ? 1 : 0;
     p.stages = smem_need(HQ, HKV, D, DV, 2) <= SMEM_LIMIT ? 2 : 1;
     p.kv_bytes = (int)region_bytes(HQ, HKV, D, DV, p.stages);
     p.splits = splits; p.part_o = part_o; p.part_ml = part_ml;
@@ -345,7 +365,17 @@ PH_EXPORT int ph_attention_talking_mma(const void* q, const void* k_base, const 
         auto kern = attention_talking_mma_kernel<DD, VV>;                                                                 \
         if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
             return fail(PH_ERR_LAUNCH, "attention_talking_mma: %zu bytes of shared memory were refused", smem);           \
-        kern<<<dim3(n_tiles, splits), HQ * 32, smem, stream>>>(p);                                                        \
+        if (p.pair) {                                                                                                     \
+            cudaLaunchConfig_t cfg = {};                                                                                  \
+            cfg.gridDim = dim3(2 * n_tiles, splits); cfg.blockDim = dim3(HQ / 2 * 32); cfg.dynamicSmemBytes = smem; cfg.stream = stream; \
+            cudaLaunchAttribute attr[1];                                                                                  \
+            attr[0].id = cudaLaunchAttributeClusterDimension;                                                             \
+            attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;                     \
+            cfg.attrs = attr; cfg.numAttrs = 1;                                                                           \
+            if (cudaLaunchKernelEx(&cfg, kern, p) != cudaSuccess) return check_launch("attention_talking_mma (cluster)"); \
+        } else {                                                                                                          \
+            kern<<<dim3(n_tiles, splits), HQ * 32, smem, stream>>>(p);                                                    \
+        }                                                                                                                 \
         if (splits > 1)                                                                                                   \
             attention_talking_merge_kernel<<<dim3(T, HQ), DV >= 64 ? 64 : 32, 0, stream>>>(part_o, part_ml, splits, sink, p.gate, gate_stride, \
                                                                                              p.out, HQ, DV);               \

@@ -349,7 +349,8 @@ public:
             int splits = (int)ctx.option_int("tile16_splits");
             if (splits < 1)
                 splits = tile16_splits(t16.count, std::max(ctx.decode_max_ctx, ctx.prefill_max_ctx), window_,
-                                       sm_count() * core.attention_talking_mma_ctas_per_sm(heads_, kv_heads_, head_dim_, value_dim_));
+                                       sm_count() * core.attention_talking_mma_ctas_per_sm(heads_, kv_heads_, head_dim_, value_dim_) /
+                                           (heads_ > 16 ? 2 : 1));      // above 16 heads a tile takes a pair of CTAs
             float *part_o = nullptr, *part_ml = nullptr;
             if (splits > 1) {
                 part_o = ws.get("attn16_part_o", {T, heads_, splits, value_dim_}, DType::F32).as<float>();
@@ -608,7 +609,8 @@ public:
             int splits = (int)ctx.option_int("tile16_splits");
             if (splits < 1)
                 splits = tile16_splits(t16.count, std::max(ctx.decode_max_ctx, ctx.prefill_max_ctx), window_,
-                                       sm_count() * core.attention_talking_mma_ctas_per_sm(heads_, kv_heads_, head_dim_, value_dim_));
+                                       sm_count() * core.attention_talking_mma_ctas_per_sm(heads_, kv_heads_, head_dim_, value_dim_) /
+                                           (heads_ > 16 ? 2 : 1));      // above 16 heads a tile takes a pair of CTAs
             float *part_o = nullptr, *part_ml = nullptr;
             if (splits > 1) {
                 part_o = ws.get("attn16_part_o", {T, heads_, splits, value_dim_}, DType::F32).as<float>();

@@ -231,8 +231,9 @@ def sharp_model(tmp, kind_m, width, seed, storage):
     return cfg, w, make_folder(tmp, cfg, w, storage)
 
 
-# windows of 9 to 200 positions and none; groups of 1 to 5; one head alone (nobody to talk to) and sixteen; heads of 16, 32,
-# 48, 64 and 96 take the tensor-core kernel in bfloat16, the others the plain one
+# windows of 9 to 200 positions and none; groups of 1 to 6; one head alone (nobody to talk to) and thirty-two (above sixteen
+# the tensor-core kernel takes a tile with a pair of CTAs); heads of 16, 32, 48, 64 and 96 take that kernel in bfloat16,
+# the others the plain one
 TALKERS = {
     "h4": (talking(4, 2, 16, 70, scale=2.0, softcap=8.0), 64),
     "h6": (talking(6, 2, 24, 33, scale=1.5, softcap=30.0), 48),
@@ -242,6 +243,8 @@ TALKERS = {
     "h5": (talking(5, 1, 32, 100, scale=1.2, softcap=10.0), 56),
     "h8": (talking(8, 2, 48, 45, scale=1.0), 72),
     "h16": (talking(16, 4, 96, 130, scale=0.7, softcap=12.0), 64),
+    "h24": (talking(24, 4, 32, 75, scale=1.1, softcap=9.0), 48),
+    "h32": (talking(32, 8, 16, 60, scale=1.6), 64),
 }
 
 
