@@ -162,15 +162,15 @@ def vokepel_config(z):
     middle layers are the repeated stretch, run once, so that the reinjection in front of it is in the step and the
     number of layer runs equals the twin's."""
     att = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"], "mask": {"size": 1024},
-           "scale": z["dim"] ** -0.5, "softcap": 30.0}
+           "scale": z["dim"] ** -0.5, "softcap": 25.0}
     left = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"], "mask": {"size": 1024},
-            "rot": {"base": 5e5, "dims": z["dim"]}, "scale": z["dim"] ** -0.5}
-    both = {"left": left, "right": {"width": z["width"]}, "left_scale": 0.6, "right_scale": 1.1}
+            "rot": {"base": 1e6, "dims": z["dim"]}, "scale": z["dim"] ** -0.5}
+    both = {"left": left, "right": {"width": z["width"]}, "left_scale": 0.8, "right_scale": 1.2}
     dense = {"kind": "dense", "ff": z["ff"]}
     layers = [{"type": "attention", "mixer": att, "mlp": dense}, {"type": "parallel", "mixer": both, "mlp": dense},
               {"type": "attention", "mixer": att, "mlp": dense}, {"type": "parallel", "mixer": both, "mlp": dense}]
-    return {"architecture": "Vokepel", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6}, "residual_mult": 0.7,
-            "logit_scale": 2.0, "logit_softcap": 30.0, "layers": layers, "loop": {"start": 1, "stop": 3, "times": 1}, "max_position": CONTEXT}
+    return {"architecture": "Vokepel", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6}, "residual_mult": 0.6,
+            "logit_scale": 1.5, "logit_softcap": 40.0, "layers": layers, "loop": {"start": 1, "stop": 3, "times": 1}, "max_position": CONTEXT}
 
 
 DESIGN_CONFIGS = {"bozosun": bozosun_config, "sizizen": sizizen_config, "zerusun": zerusun_config, "vokepel": vokepel_config}

@@ -290,9 +290,9 @@ def test_talking_attention_alone_whole_cut_decoded_and_batched(tmp_path, which, 
 
 # the left side alone: heads of 48, 64 and 128 (sizes the tensor-core kernel takes) and others; values narrower and wider
 LEFTS = {
-    "d64": (left_side(4, 2, 64, 64, 70, 32, base=300.0, scale=0.6), 64),
+    "d64": (left_side(4, 1, 64, 64, 70, 32, base=300.0, scale=0.6), 64),
     "d128": (left_side(2, 1, 128, 128, 33, 128, base=1e4, scale=0.4), 48),
-    "d24": (left_side(3, 3, 24, 40, 50, 2, base=5e5, scale=1.0), 64),
+    "d24": (left_side(3, 3, 24, 40, 50, 2, base=2e5, scale=1.0), 64),
     "d16": (left_side(8, 2, 16, 8, None, 0, scale=1.2), 40),
     "d64v": (left_side(4, 4, 64, 32, 100, 16, base=77.0, scale=0.5), 40),
     "d48": (left_side(6, 2, 48, 48, 17, 48, base=1e3, scale=0.7), 72),

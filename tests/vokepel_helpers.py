@@ -65,7 +65,7 @@ CONFIG_B = config(40, 70, [
 
 # wider layers, stored in bfloat16: heads of 64 on the left side, six talking heads of 32, the whole model repeated once
 CONFIG_C = config(128, 200, [
-    (pair(left_side(4, 1, 64, 32, 40, 32, base=5e5), 160, 0.7, 0.9), dense(256)),
+    (pair(left_side(4, 1, 64, 32, 40, 32, base=3e5), 160, 0.7, 0.9), dense(256)),
     (talking(6, 2, 32, 40, scale=0.2, softcap=15.0), dense(192)),
     (pair(left_side(2, 1, 32, 64, 70, 0), 96, 1.2, 0.4), None),
 ], loop=(0, 3, 1), eps=1e-6, mult=0.8, logit_softcap=25.0)
