@@ -483,6 +483,33 @@ def test_key_splits_of_the_tile_kernel_agree_with_the_plain_implementation(model
         eng.close()
 
 
+def test_a_sink_survives_the_merges_of_the_tcgen05_and_tma_kernels(tmp_path):
+    """Heads of 128 with a sink take the tcgen05 prompt kernel and the TMA decode kernel; with their keys shared between CTAs
+    the sink joins the sum in the merge, once."""
+    from purhie_b200.engine import StepEntry
+    cfg = config(64, 40, [(pair(left_side(2, 1, 128, 128, 150, 64, base=1e4, scale=0.3), 32, 1.0, 0.2), dense(48)),
+                          (pair(left_side(4, 2, 128, 128, None, 128, base=300.0, scale=0.2), 24, 0.9, 0.3), None)], mult=0.9)
+    w = draw_weights(cfg, 12, std=0.5)
+    for name in ("l0.mix.left.sink", "l1.mix.left.sink"):
+        w[name] = w[name] + 3.0                                  # sinks that take a good part of the weight
+    folder = make_folder(tmp_path, cfg, w, "BF16")
+    toks = tokens(330, cfg["vocab"], 4)
+    wd = f64(w)
+    ref = P.forward(cfg, wd, toks)
+    without = P.forward(cfg, dict(wd, **{n: wd[n] - 1e30 for n in ("l0.mix.left.sink", "l1.mix.left.sink")}), toks)
+    assert np.abs(without - ref).max() > 3 * TOL["bfloat16"] * np.abs(ref).max()
+    for options in ({}, {"decode_splits": 3, "prefill_splits": 2}, {"decode_splits": 8, "prefill_splits": 5}, {"sink_kernel": "tile"}):
+        eng = engine_for(folder, "bfloat16", max_tokens=1024, step_options=options)
+        close(run_cut(eng, "whole", toks, []), ref, TOL["bfloat16"])
+        close(run_cut(eng, "tail", toks, [2, 270] + [1] * 58), ref, TOL["bfloat16"])
+        eng.add_request("a"); eng.add_request("b")
+        eng.step([StepEntry("a", toks[:200], [])])
+        out = eng.step([StepEntry("a", toks[200:201], [0]), StepEntry("b", toks[:140], list(range(140)))])
+        close(out[:1], ref[200:201], TOL["bfloat16"])
+        close(out[1:], ref[:140], TOL["bfloat16"])
+        eng.close()
+
+
 # ---- generation -----------------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("name,dtype", [("A", "float32"), ("C", "float32")])
 def test_greedy_generation_through_the_entry_point_and_the_scheduler(models, name, dtype):
