@@ -349,3 +349,103 @@ def sample_chain(logits: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) ->
         raise KernelError("sample_chain: one 24-byte record and one output per row")
     call("core", "ph_sample_chain", _ptr(logits), R, V, _ptr(rows), _ptr(out), _stream())
     return out
+
+
+# ---- attention whose heads talk before the softmax, the recurrent unit, and their small companions -------------------
+register_signatures("core", {
+    "ph_attention_generic_sink": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_longlong, c_int, c_void_p, c_int, c_void_p, c_void_p,
+                                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p],
+    "ph_attention_talking": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_longlong, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p, c_void_p,
+                             c_void_p, c_void_p, c_int, c_longlong, c_void_p],
+    "ph_attention_talking_mma": [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                 c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p, c_void_p,
+                                 c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p],
+    "ph_attention_talking_mma_supports": [c_int, c_int, c_int, c_int],
+    "ph_min_gru_scan": [c_void_p, c_int, c_int, c_longlong, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                        c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+    "ph_pair_sum": [c_void_p, c_int, c_int, c_longlong, c_float, c_void_p, c_int, c_int, c_longlong, c_float, c_void_p, c_longlong, c_void_p],
+    "ph_scale_softcap": [c_void_p, c_longlong, c_float, c_float, c_void_p],
+    "ph_add_scaled_rmsnorm": [c_void_p, c_void_p, c_int, c_int, c_longlong, c_void_p, c_float, c_void_p, c_int, c_int, c_void_p, c_int, c_int,
+                              c_float, c_void_p],
+})
+
+
+def attention_generic_sink(q, k_base, v_base, page_stride, page_size, block_table, row_seg, positions, out, sink, *, num_heads,
+                           num_kv_heads, head_dim, window, scale) -> torch.Tensor:
+    """attention_generic with exp(sink[h]) in every row's denominator."""
+    _need(q, "q"); _need(out, "out"); _need(sink, "sink", torch.float32)
+    T = positions.numel()
+    call("core", "ph_attention_generic_sink", _ptr(q), _code(q.dtype), _ptr(k_base), _ptr(v_base), _code(k_base.dtype), page_stride,
+         page_size, _ptr(block_table), block_table.shape[-1], _ptr(row_seg), _ptr(positions), _ptr(out), _code(out.dtype), T,
+         num_heads, num_kv_heads, head_dim, int(window or 0), float(scale), 0, 0, 0, _ptr(sink), _stream())
+    return out
+
+
+def attention_talking(q, k_base, v_base, page_stride, page_size, block_table, row_seg, positions, out, *, num_heads, num_kv_heads,
+                      head_dim, window, scale, cap=0.0, slope=None, rate=None, talk=None, sink=None, gate=None) -> torch.Tensor:
+    """The plain kernel: scores capped, biased by the distance and mixed over the heads before the softmax."""
+    _need(q, "q"); _need(out, "out")
+    T = positions.numel()
+    call("core", "ph_attention_talking", _ptr(q), _code(q.dtype), _ptr(k_base), _ptr(v_base), _code(k_base.dtype), page_stride, page_size,
+         _ptr(block_table), block_table.shape[-1], _ptr(row_seg), _ptr(positions), _ptr(out), _code(out.dtype), T, num_heads, num_kv_heads,
+         head_dim, head_dim, int(window or 0), 0, float(scale), float(cap), _ptr(slope), _ptr(rate), _ptr(talk), _ptr(sink), _ptr(gate),
+         _code(gate.dtype) if gate is not None else 0, gate.shape[-1] if gate is not None else 0, _stream())
+    return out
+
+
+def attention_talking_mma_supports(num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int) -> bool:
+    f, _ = _fn("core", "ph_attention_talking_mma_supports")
+    return bool(f(num_heads, num_kv_heads, head_dim, value_dim))
+
+
+def attention_talking_mma(q, k_base, v_base, page_stride, page_size, block_table, seg_start, seg_ctx, tile_seg, tile_first, out, *,
+                          num_heads, num_kv_heads, head_dim, window, scale, cap=0.0, slope=None, rate=None, talk=None, sink=None,
+                          gate=None, splits=1) -> torch.Tensor:
+    """The tensor-core kernel (bfloat16): tiles of 16 rows of one request, all heads per tile."""
+    _need(q, "q", torch.bfloat16); _need(out, "out", torch.bfloat16)
+    T = q.shape[0]
+    part_o = torch.empty((T, num_heads, splits, head_dim), dtype=torch.float32, device=q.device) if splits > 1 else None
+    part_ml = torch.empty((T, num_heads, splits, 2), dtype=torch.float32, device=q.device) if splits > 1 else None
+    call("core", "ph_attention_talking_mma", _ptr(q), _ptr(k_base), _ptr(v_base), page_stride, page_size, _ptr(block_table),
+         block_table.shape[-1], _ptr(seg_start), _ptr(seg_ctx), _ptr(tile_seg), _ptr(tile_first), tile_seg.numel(), _ptr(out), num_heads,
+         num_kv_heads, head_dim, head_dim, int(window or 0), 0, float(scale), float(cap), _ptr(slope), _ptr(rate), _ptr(talk), _ptr(sink),
+         _ptr(gate), gate.shape[-1] if gate is not None else 0, splits, T, _ptr(part_o), _ptr(part_ml), _stream())
+    return out
+
+
+def min_gru_scan(rows: torch.Tensor, z_bias, x_bias, state, seg_start, seg_slot, out, chunks=None, seg_chunks=None) -> torch.Tensor:
+    """rows [splits, T, 3 W] = [a_z | a_x | a_g]; state [slots, W] float32 (updated in place); out [T, W]."""
+    _need(rows, "rows"); _need(state, "state", torch.float32); _need(out, "out")
+    splits, T, width3 = rows.shape
+    W = width3 // 3
+    n_chunks = 0 if chunks is None else chunks.numel() // 4
+    carry = torch.empty((3, max(n_chunks, 1), W), dtype=torch.float32, device=rows.device)
+    call("core", "ph_min_gru_scan", _ptr(rows), _code(rows.dtype), splits, T * width3, width3, _ptr(z_bias), _ptr(x_bias), _ptr(state),
+         _ptr(seg_start), _ptr(seg_slot), seg_slot.numel(), T, W, _ptr(chunks), n_chunks, _ptr(seg_chunks), _ptr(carry), _ptr(out),
+         _code(out.dtype), _stream())
+    return out
+
+
+def pair_sum(a: torch.Tensor, fa: float, b: torch.Tensor, fb: float, out: torch.Tensor) -> torch.Tensor:
+    """out = fa * (sum of a's parts) + fb * (sum of b's parts); a, b [splits, n]."""
+    _need(a, "a"); _need(b, "b"); _need(out, "out", torch.float32)
+    n = out.numel()
+    call("core", "ph_pair_sum", _ptr(a), _code(a.dtype), a.numel() // n, n, float(fa), _ptr(b), _code(b.dtype), b.numel() // n, n, float(fb),
+         _ptr(out), n, _stream())
+    return out
+
+
+def scale_softcap(y: torch.Tensor, scale: float, cap: float) -> torch.Tensor:
+    _need(y, "y", torch.float32)
+    call("core", "ph_scale_softcap", _ptr(y), y.numel(), float(scale), float(cap), _stream())
+    return y
+
+
+def add_scaled_rmsnorm(x, add, weight, eps, y, add_scale, *, add_splits=1, write_x=True) -> torch.Tensor:
+    """x += add_scale * (sum of add's parts); y = rmsnorm(x) * weight."""
+    _need(x, "x", torch.float32); _need(add, "add"); _need(y, "y")
+    T, E = x.shape
+    call("core", "ph_add_scaled_rmsnorm", _ptr(x), _ptr(add), _code(add.dtype), add_splits, T * E, _ptr(weight), float(eps), None, T, E,
+         _ptr(y), _code(y.dtype), 1 if write_x else 0, float(add_scale), _stream())
+    return y
