@@ -12,9 +12,10 @@
 // (running maximum and sum per row) and O_h += P_h V_kv(h) on the tensor cores with P rounded to bfloat16, as in the
 // other tensor-core attention kernels.  The sink joins the denominator at the end; the gate multiplies the output.
 // Q tiles of all heads pass through the shared memory that the keys use afterwards.
-// More than 16 heads (up to 32): a cluster of two CTAs takes a tile, each CTA half of the heads with their kv heads; the
-// scores of the other half are read from the partner's shared memory (distributed shared memory), and the two barriers of
-// a block become barriers of the cluster.  Both CTAs walk the same key blocks, so they meet the same barriers.
+// More than 16 heads (up to 32): a cluster of two CTAs takes a tile, each CTA half of the heads with their kv heads; a
+// warp writes its head's scores into its own CTA's shared memory and into the partner's (distributed shared memory: 2 KB
+// cross per warp and block, where reading the partner's half from there would be 32 KB), and the two barriers of a block
+// become barriers of the cluster.  Both CTAs walk the same key blocks, so they meet the same barriers.
 #include "attention_mma.cuh"
 
 #include <cooperative_groups.h>
@@ -69,10 +70,10 @@ __global__ void __launch_bounds__(MAX_HEADS * 32) attention_talking_mma_kernel(c
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, threads = blockDim.x;
     const int h = warp, g = h / (HQ / HKV);                   // within this CTA
     const uint32_t region = smem_u32(smem);
-    float* sc = reinterpret_cast<float*>(smem + p.kv_bytes);  // [HQ][BM][SP]: this CTA's heads' scores
-    float* tk = sc + (size_t)HQ * BM * SP;                    // [HQ][HA]: this CTA's rows of the mix
+    float* sc = reinterpret_cast<float*>(smem + p.kv_bytes);  // [HA][BM][SP]: all heads' scores, the partner's half written by the partner
+    float* tk = sc + (size_t)HA * BM * SP;                    // [HQ][HA]: this CTA's rows of the mix
     float* bias = tk + (size_t)HQ * HA + (size_t)h * BIAS_N;  // this head's distance bias for the block's 47 distances
-    const float* sc_other = p.pair ? cluster.map_shared_rank(sc, rank ^ 1) : sc;      // the partner's scores
+    float* sc_other = p.pair ? cluster.map_shared_rank(sc, rank ^ 1) : nullptr;      // the same array in the partner's shared memory
 
     const int tile = p.pair ? blockIdx.x / 2 : blockIdx.x;
     const int seg = p.tile_seg[tile], first = p.tile_first[tile];
@@ -182,8 +183,12 @@ __global__ void __launch_bounds__(MAX_HEADS * 32) attention_talking_mma_kernel(c
 #pragma unroll
             for (int nt = 0; nt < BK / 8; ++nt) {
                 const int c = nt * 8 + (lane & 3) * 2;
-                *reinterpret_cast<float2*>(sc + ((size_t)h * BM + r0) * SP + c) = make_float2(s[nt][0], s[nt][1]);
-                *reinterpret_cast<float2*>(sc + ((size_t)h * BM + r1) * SP + c) = make_float2(s[nt][2], s[nt][3]);
+                *reinterpret_cast<float2*>(sc + ((size_t)(h0 + h) * BM + r0) * SP + c) = make_float2(s[nt][0], s[nt][1]);
+                *reinterpret_cast<float2*>(sc + ((size_t)(h0 + h) * BM + r1) * SP + c) = make_float2(s[nt][2], s[nt][3]);
+                if (sc_other) {
+                    *reinterpret_cast<float2*>(sc_other + ((size_t)(h0 + h) * BM + r0) * SP + c) = make_float2(s[nt][0], s[nt][1]);
+                    if (upper) *reinterpret_cast<float2*>(sc_other + ((size_t)(h0 + h) * BM + r1) * SP + c) = make_float2(s[nt][2], s[nt][3]);
+                }
             }
             if (p.pair) cluster.sync(); else __syncthreads();
             // the mix in packed pairs: a thread's two neighbouring columns are one 64-bit accumulator
@@ -194,7 +199,7 @@ __global__ void __launch_bounds__(MAX_HEADS * 32) attention_talking_mma_kernel(c
             for (int j = 0; j < HA; ++j) {                    // over all heads, in the order of the heads whichever CTA holds them
                 unsigned long long ww;
                 asm("mov.b64 %0, {%1, %1};" : "=l"(ww) : "f"(tk[h * HA + j]));
-                const float* from = (j >= h0 && j < h0 + HQ) ? sc + (size_t)(j - h0) * BM * SP : sc_other + (size_t)(j - (h0 ? 0 : HQ)) * BM * SP;
+                const float* from = sc + (size_t)j * BM * SP;
 #pragma unroll
                 for (int nt = 0; nt < BK / 8; ++nt) {
                     const int c = nt * 8 + (lane & 3) * 2;
@@ -302,7 +307,7 @@ size_t region_bytes(int HQ, int HKV, int D, int DV, int stages) {
 }
 size_t smem_need(int HQ, int HKV, int D, int DV, int stages) {
     const int HL = paired(HQ) ? HQ / 2 : HQ;
-    return region_bytes(HQ, HKV, D, DV, stages) + ((size_t)HL * BM * SP + (size_t)HL * HQ + (size_t)HL * BIAS_N) * sizeof(float);
+    return region_bytes(HQ, HKV, D, DV, stages) + ((size_t)HQ * BM * SP + (size_t)HL * HQ + (size_t)HL * BIAS_N) * sizeof(float);
 }
 constexpr size_t SMEM_LIMIT = 227 * 1024;
 bool instantiated(int D, int DV) {
