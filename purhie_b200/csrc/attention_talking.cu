@@ -15,7 +15,8 @@
 //                         is given), o_h = sum_p w_hp v_kv(h)p, and o_h * sigmoid(gate_h) when a gate row is given.
 //                         Because every head's score enters every head's softmax, one block handles all heads of a row:
 //                         warp g scores head g for 32 keys at a time (a key per lane), the block exchanges the scores
-//                         through shared memory, and warp h mixes, runs the online softmax and sums the values of head h.
+//                         through shared memory, and warp h mixes, runs the online softmax and sums the values of head h
+//                         (above 32 heads a warp takes two or four heads in turn).
 // All arithmetic is float32 in an order that depends on (z, window) only, never on how a request was cut into steps or
 // on what else is in the batch.  Cache addressing as in qk_norm_rope.cu.
 #include "common.cuh"
@@ -27,9 +28,10 @@ namespace {
 using namespace ph;
 
 constexpr int MAX_DV = 512;      // widest value row
-constexpr int MAX_HEADS = 32;    // a warp per head, one block per row
+constexpr int MAX_HEADS = 64;    // a block per row: a warp per head up to 32 heads, two or four heads per warp above
 
-template <typename TQ, typename TKV, typename TG, typename TO>
+// HPW: heads per warp.  A block has ceil(HQ / HPW) warps; warp w takes the heads w, w + warps, ... (at most HPW of them).
+template <typename TQ, typename TKV, typename TG, typename TO, int HPW>
 __global__ void attention_talking_kernel(const TQ* __restrict__ q, const TKV* __restrict__ k_base, const TKV* __restrict__ v_base,
                                          long long page_stride, int page_size, const int32_t* __restrict__ block_table, int table_stride,
                                          const int32_t* __restrict__ row_seg, const int32_t* __restrict__ positions,
@@ -41,9 +43,9 @@ __global__ void attention_talking_kernel(const TQ* __restrict__ q, const TKV* __
     float* qs = smem;                          // [HQ][D]
     float* sc = qs + (size_t)HQ * D;           // [HQ][32]: the heads' own scores of the current 32 keys
     float* tk = sc + (size_t)HQ * 32;          // [HQ][HQ]
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x, h = warp;
-    const int g = h / (HQ / HKV);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    const int t = blockIdx.x;
+    const int group = HQ / HKV;
     const int z = positions[t];
     const int lo = first_seen(z, window, chunk);
     const int32_t* table = block_table + (size_t)row_seg[t] * table_stride;
@@ -51,75 +53,102 @@ __global__ void attention_talking_kernel(const TQ* __restrict__ q, const TKV* __
     for (int i = threadIdx.x; i < HQ * D; i += blockDim.x) qs[i] = to_float<TQ>(qr[i]);
     if (talk)
         for (int i = threadIdx.x; i < HQ * HQ; i += blockDim.x) tk[i] = talk[i];
-    const float b1 = r1 ? r1[h] : 0.0f, b2 = r2 ? r2[h] : 0.0f;
     __syncthreads();
 
-    float m = -INFINITY, l = 0.0f;
-    float acc[MAX_DV / 32];
+    float m[HPW], l[HPW];
+    float acc[HPW][MAX_DV / 32];
 #pragma unroll
-    for (int i = 0; i < MAX_DV / 32; ++i) acc[i] = 0.0f;
-    const float* qh = qs + (size_t)h * D;
+    for (int u = 0; u < HPW; ++u) {
+        m[u] = -INFINITY; l[u] = 0.0f;
+#pragma unroll
+        for (int i = 0; i < MAX_DV / 32; ++i) acc[u][i] = 0.0f;
+    }
 
     for (int base = lo; base <= z; base += 32) {
         const int p = base + lane;
         const bool seen = p <= z;
-        float s = 0.0f;
-        const TKV* vrow = nullptr;
-        if (seen) {
-            const int page = table[p / page_size];
-            const size_t at = (size_t)g * page_size + p % page_size;
-            const TKV* krow = k_base + (size_t)page * page_stride + at * D;
-            vrow = v_base + (size_t)page * page_stride + at * DV;
-            float dot = 0.0f;
-            for (int d = 0; d < D; ++d) dot += qh[d] * to_float<TKV>(krow[d]);
-            s = dot * scale;
-            if (cap > 0.0f) s = cap * tanhf(s / cap);
-            if (r1) s -= b1 * log1pf(b2 * (float)(z - p));
-        }
-        if (talk) {
-            sc[h * 32 + lane] = s;
-            __syncthreads();
-            float mixed = 0.0f;
-            for (int j = 0; j < HQ; ++j) mixed += tk[h * HQ + j] * sc[j * 32 + lane];
-            s = mixed;
-        }
-        if (!seen) s = -INFINITY;
-        const float m_new = fmaxf(m, warp_max(s));
-        const float pexp = seen ? expf(s - m_new) : 0.0f;
-        const float corr = expf(m - m_new);            // m = -inf on the first block: corr = 0, l and acc are 0
-        l = l * corr + warp_sum(pexp);
+        int page = 0, off = 0;
+        if (seen) { page = table[p / page_size]; off = p % page_size; }
+        float s[HPW];
 #pragma unroll
-        for (int i = 0; i < MAX_DV / 32; ++i) acc[i] *= corr;
-        const int n = (z - base + 1) < 32 ? (z - base + 1) : 32;
-        for (int j = 0; j < n; ++j) {
-            const float pj = __shfl_sync(0xffffffffu, pexp, j);
-            const unsigned long long vp = __shfl_sync(0xffffffffu, (unsigned long long)vrow, j);
-            const TKV* vj = (const TKV*)vp;
-#pragma unroll
-            for (int i = 0; i < MAX_DV / 32; ++i) {
-                const int d = lane + 32 * i;
-                if (d < DV) acc[i] += pj * to_float<TKV>(vj[d]);
+        for (int u = 0; u < HPW; ++u) {
+            const int h = warp + u * warps;
+            s[u] = 0.0f;
+            if (h < HQ && seen) {
+                const TKV* krow = k_base + (size_t)page * page_stride + ((size_t)(h / group) * page_size + off) * D;
+                const float* qh = qs + (size_t)h * D;
+                float dot = 0.0f;
+                for (int d = 0; d < D; ++d) dot += qh[d] * to_float<TKV>(krow[d]);
+                float v = dot * scale;
+                if (cap > 0.0f) v = cap * tanhf(v / cap);
+                if (r1) v -= r1[h] * log1pf(r2[h] * (float)(z - p));
+                s[u] = v;
             }
         }
-        m = m_new;
+        if (talk) {
+#pragma unroll
+            for (int u = 0; u < HPW; ++u) {
+                const int h = warp + u * warps;
+                if (h < HQ) sc[h * 32 + lane] = s[u];
+            }
+            __syncthreads();
+#pragma unroll
+            for (int u = 0; u < HPW; ++u) {
+                const int h = warp + u * warps;
+                if (h >= HQ) continue;
+                float mixed = 0.0f;
+                for (int j = 0; j < HQ; ++j) mixed += tk[h * HQ + j] * sc[j * 32 + lane];
+                s[u] = mixed;
+            }
+        }
+        const int n = (z - base + 1) < 32 ? (z - base + 1) : 32;
+#pragma unroll
+        for (int u = 0; u < HPW; ++u) {
+            const int h = warp + u * warps;
+            if (h >= HQ) continue;                         // the whole warp: h depends on the warp alone
+            const float sv = seen ? s[u] : -INFINITY;
+            const float m_new = fmaxf(m[u], warp_max(sv));
+            const float pexp = seen ? expf(sv - m_new) : 0.0f;
+            const float corr = expf(m[u] - m_new);         // m = -inf on the first block: corr = 0, l and acc are 0
+            l[u] = l[u] * corr + warp_sum(pexp);
+#pragma unroll
+            for (int i = 0; i < MAX_DV / 32; ++i) acc[u][i] *= corr;
+            const TKV* vrow = seen ? v_base + (size_t)page * page_stride + ((size_t)(h / group) * page_size + off) * DV : nullptr;
+            for (int j = 0; j < n; ++j) {
+                const float pj = __shfl_sync(0xffffffffu, pexp, j);
+                const unsigned long long vp = __shfl_sync(0xffffffffu, (unsigned long long)vrow, j);
+                const TKV* vj = (const TKV*)vp;
+#pragma unroll
+                for (int i = 0; i < MAX_DV / 32; ++i) {
+                    const int d = lane + 32 * i;
+                    if (d < DV) acc[u][i] += pj * to_float<TKV>(vj[d]);
+                }
+            }
+            m[u] = m_new;
+        }
         if (talk) __syncthreads();                     // the scores are read before the next block overwrites them
     }
-    if (sink) {
-        const float sk = sink[h], top = fmaxf(m, sk), corr = expf(m - top);
-        l = l * corr + expf(sk - top);
 #pragma unroll
-        for (int i = 0; i < MAX_DV / 32; ++i) acc[i] *= corr;
-    }
-    TO* o = out + ((size_t)t * HQ + h) * DV;
-    const TG* gr = gate ? gate + (size_t)t * gate_stride + (size_t)h * DV : nullptr;
-    const float inv = 1.0f / l;
+    for (int u = 0; u < HPW; ++u) {
+        const int h = warp + u * warps;
+        if (h >= HQ) continue;
+        if (sink) {
+            const float sk = sink[h], top = fmaxf(m[u], sk), corr = expf(m[u] - top);
+            l[u] = l[u] * corr + expf(sk - top);
 #pragma unroll
-    for (int i = 0; i < MAX_DV / 32; ++i) {
-        const int d = lane + 32 * i;
-        if (d < DV) {
-            float v = acc[i] * inv;
-            if (gr) v *= 1.0f / (1.0f + expf(-to_float<TG>(gr[d])));
-            o[d] = from_float<TO>(v);
+            for (int i = 0; i < MAX_DV / 32; ++i) acc[u][i] *= corr;
+        }
+        TO* o = out + ((size_t)t * HQ + h) * DV;
+        const TG* gr = gate ? gate + (size_t)t * gate_stride + (size_t)h * DV : nullptr;
+        const float inv = 1.0f / l[u];
+#pragma unroll
+        for (int i = 0; i < MAX_DV / 32; ++i) {
+            const int d = lane + 32 * i;
+            if (d < DV) {
+                float v = acc[u][i] * inv;
+                if (gr) v *= 1.0f / (1.0f + expf(-to_float<TG>(gr[d])));
+                o[d] = from_float<TO>(v);
+            }
         }
     }
 }
@@ -255,16 +284,23 @@ PH_EXPORT int ph_attention_talking(const void* q, int q_dtype, const void* k_bas
     if (smem > 200 * 1024) return fail(PH_ERR_UNSUPPORTED, "attention_talking: %d heads of %d do not fit shared memory", HQ, D);
     if (T == 0) return PH_OK;
     if (!gate) gate_dtype = q_dtype;
+    // (two heads per warp take 94 registers a thread and four take 127: 20 and 16 warps are what an SM's registers hold)
+    const int hpw = HQ <= 32 ? 1 : HQ <= 40 ? 2 : 4, warps = (HQ + hpw - 1) / hpw;
+#define LAUNCH_N(TQ, TKV, TG, TO, N)                                                                                              \
+    do {                                                                                                                          \
+        auto kern = attention_talking_kernel<TQ, TKV, TG, TO, N>;                                                                 \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                 \
+        kern<<<T, warps * 32, smem, stream>>>((const TQ*)q, (const TKV*)k_base, (const TKV*)v_base, page_stride, page_size, block_table, \
+                                              table_stride, row_seg, positions, (TO*)out, HQ, HKV, D, DV, window, chunk, scale, cap, \
+                                              r1, r2, talk, sink, (const TG*)gate, gate_stride);                                  \
+    } while (0)
 #define LAUNCH(TQ, TKV, TG, TO)                                                                                                   \
     do {                                                                                                                          \
-        auto kern = attention_talking_kernel<TQ, TKV, TG, TO>;                                                                    \
-        if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                 \
-        kern<<<T, HQ * 32, smem, stream>>>((const TQ*)q, (const TKV*)k_base, (const TKV*)v_base, page_stride, page_size, block_table, \
-                                           table_stride, row_seg, positions, (TO*)out, HQ, HKV, D, DV, window, chunk, scale, cap, \
-                                           r1, r2, talk, sink, (const TG*)gate, gate_stride);                                     \
+        if (hpw == 1) LAUNCH_N(TQ, TKV, TG, TO, 1); else if (hpw == 2) LAUNCH_N(TQ, TKV, TG, TO, 2); else LAUNCH_N(TQ, TKV, TG, TO, 4); \
     } while (0)
     PH_DISPATCH(q_dtype, TQ, PH_DISPATCH(kv_dtype, TKV, PH_DISPATCH(gate_dtype, TG, PH_DISPATCH(out_dtype, TO, LAUNCH(TQ, TKV, TG, TO)))));
 #undef LAUNCH
+#undef LAUNCH_N
     return check_launch("attention_talking");
 }
 

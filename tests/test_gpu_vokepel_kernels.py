@@ -54,7 +54,8 @@ def extras(HQ, D, T, dtype, seed, with_all=True):
 
 
 @pytest.mark.parametrize("HQ,HKV,D,page_size,window,cap", [
-    (4, 2, 16, 16, None, 5.0), (6, 3, 48, 8, 24, 20.0), (3, 1, 80, 5, 7, 0.0), (12, 4, 32, 16, 100, 3.0), (1, 1, 40, 16, 33, 8.0)])
+    (4, 2, 16, 16, None, 5.0), (6, 3, 48, 8, 24, 20.0), (3, 1, 80, 5, 7, 0.0), (12, 4, 32, 16, 100, 3.0), (1, 1, 40, 16, 33, 8.0),
+    (36, 6, 8, 16, 50, 4.0), (64, 16, 16, 8, None, 9.0)])            # two and four heads per warp
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_attention_talking_plain_kernel(HQ, HKV, D, page_size, window, cap, dtype):
     from purhie_b200.csrc import ops
